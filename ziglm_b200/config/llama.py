@@ -1,0 +1,299 @@
+"""Typed configuration of the Llama-style dense decoder, read from config.json.
+
+Keys and defaults follow what the reference reads in ``parseHFConfig``
+(src/safetensors.zig:482-596) and ``ModelParams.initComputed``
+(src/types.zig:246-285): hidden_size, intermediate_size, num_attention_heads,
+num_key_value_heads (default: num_attention_heads), num_hidden_layers,
+vocab_size, rms_norm_eps (default 1e-5), rope_theta (default 10000),
+max_position_embeddings (default 2048), head_dim (default hidden/heads).
+The reference parses rope_theta but never uses it and knows no rope_scaling,
+attention_bias, tie_word_embeddings or eos ids; those are read here because the
+architecture's own config.json carries them.
+
+Nothing is inferred from tensor shapes (the reference overwrites its parameters
+from shapes, src/safetensors.zig:181-252); shapes are checked against this
+configuration by the weight loader instead.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import dataclass, asdict
+from typing import Any, Dict, Mapping, Optional, Tuple
+
+from .spec import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec,
+                   PositionSpec)
+
+
+class ConfigError(ValueError):
+    """config.json is missing a key, or a value is of the wrong kind or out of range."""
+
+
+def _need_int(d: Mapping[str, Any], key: str, default: Optional[int] = None, minimum: int = 1) -> int:
+    v = d.get(key, default)
+    if v is None:
+        raise ConfigError(f"config.json: required key '{key}' is missing")
+    if isinstance(v, bool) or not isinstance(v, int):
+        raise ConfigError(f"config.json: '{key}' must be an integer, found {v!r}")
+    if v < minimum:
+        raise ConfigError(f"config.json: '{key}' must be >= {minimum}, found {v}")
+    return v
+
+
+def _need_float(d: Mapping[str, Any], key: str, default: Optional[float] = None) -> float:
+    v = d.get(key, default)
+    if v is None:
+        raise ConfigError(f"config.json: required key '{key}' is missing")
+    if isinstance(v, bool) or not isinstance(v, (int, float)):
+        raise ConfigError(f"config.json: '{key}' must be a number, found {v!r}")
+    v = float(v)
+    if not math.isfinite(v) or v <= 0.0:
+        raise ConfigError(f"config.json: '{key}' must be a positive finite number, found {v}")
+    return v
+
+
+def _need_bool(d: Mapping[str, Any], key: str, default: bool) -> bool:
+    v = d.get(key, default)
+    if v is None:
+        return default
+    if not isinstance(v, bool):
+        raise ConfigError(f"config.json: '{key}' must be true or false, found {v!r}")
+    return v
+
+
+def _token_ids(d: Mapping[str, Any], key: str) -> Tuple[int, ...]:
+    v = d.get(key)
+    if v is None:
+        return ()
+    items = v if isinstance(v, (list, tuple)) else [v]
+    out = []
+    for t in items:
+        if isinstance(t, bool) or not isinstance(t, int) or t < 0:
+            raise ConfigError(f"config.json: '{key}' must be a token id or a list of them, found {v!r}")
+        out.append(t)
+    return tuple(out)
+
+
+@dataclass(frozen=True)
+class RopeScaling:
+    """``rope_scaling`` of kind "llama3": low frequencies are slowed by ``factor``."""
+    rope_type: str
+    factor: float
+    low_freq_factor: float
+    high_freq_factor: float
+    original_max_position_embeddings: int
+
+    @classmethod
+    def from_dict(cls, d: Optional[Mapping[str, Any]]) -> Optional["RopeScaling"]:
+        if d is None:
+            return None
+        if not isinstance(d, Mapping):
+            raise ConfigError(f"config.json: 'rope_scaling' must be an object or null, found {d!r}")
+        kind = d.get("rope_type", d.get("type"))
+        if kind in (None, "default"):
+            return None
+        if kind != "llama3":
+            raise ConfigError(f"config.json: rope_scaling of type {kind!r} is not supported (only 'llama3')")
+        s = cls(
+            rope_type="llama3",
+            factor=_need_float(d, "factor"),
+            low_freq_factor=_need_float(d, "low_freq_factor"),
+            high_freq_factor=_need_float(d, "high_freq_factor"),
+            original_max_position_embeddings=_need_int(d, "original_max_position_embeddings"),
+        )
+        if s.high_freq_factor <= s.low_freq_factor:
+            raise ConfigError("config.json: rope_scaling.high_freq_factor must exceed low_freq_factor")
+        return s
+
+    def to_dict(self) -> Dict[str, Any]:
+        return asdict(self)
+
+
+@dataclass(frozen=True)
+class LlamaConfig:
+    architecture: str
+    hidden_size: int
+    intermediate_size: int
+    num_hidden_layers: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    head_dim: int
+    vocab_size: int
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[RopeScaling] = None
+    max_position_embeddings: int = 2048
+    tie_word_embeddings: bool = False
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    hidden_act: str = "silu"
+    bos_token_id: Optional[int] = None
+    eos_token_ids: Tuple[int, ...] = ()
+
+    ARCHITECTURE = "LlamaForCausalLM"
+
+    # ------------------------------------------------------------------ reading
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "LlamaConfig":
+        if not isinstance(d, Mapping):
+            raise ConfigError("config.json must hold a JSON object")
+        arch = d.get("architectures")
+        if not (isinstance(arch, (list, tuple)) and arch and isinstance(arch[0], str)):
+            raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        hidden = _need_int(d, "hidden_size")
+        heads = _need_int(d, "num_attention_heads")
+        kv_heads = _need_int(d, "num_key_value_heads", default=heads)
+        if d.get("head_dim") is None:
+            if hidden % heads:
+                raise ConfigError(
+                    f"config.json: hidden_size {hidden} is not a multiple of num_attention_heads {heads} "
+                    "and no head_dim is given")
+            head_dim = hidden // heads
+        else:
+            head_dim = _need_int(d, "head_dim")
+        if heads % kv_heads:
+            raise ConfigError(
+                f"config.json: num_attention_heads {heads} is not a multiple of num_key_value_heads {kv_heads}")
+        if head_dim % 2:
+            raise ConfigError(f"config.json: head_dim {head_dim} must be even for rotary positions")
+        act = d.get("hidden_act", "silu")
+        if act not in ("silu", "swish"):
+            raise ConfigError(f"config.json: hidden_act {act!r} is not supported by this architecture (silu)")
+        bos = d.get("bos_token_id")
+        if bos is not None and (isinstance(bos, bool) or not isinstance(bos, int)):
+            raise ConfigError(f"config.json: 'bos_token_id' must be an integer, found {bos!r}")
+        cfg = cls(
+            architecture=arch[0],
+            hidden_size=hidden,
+            intermediate_size=_need_int(d, "intermediate_size"),
+            num_hidden_layers=_need_int(d, "num_hidden_layers"),
+            num_attention_heads=heads,
+            num_key_value_heads=kv_heads,
+            head_dim=head_dim,
+            vocab_size=_need_int(d, "vocab_size"),
+            rms_norm_eps=_need_float(d, "rms_norm_eps", default=1e-5),
+            rope_theta=_need_float(d, "rope_theta", default=10000.0),
+            rope_scaling=RopeScaling.from_dict(d.get("rope_scaling")),
+            max_position_embeddings=_need_int(d, "max_position_embeddings", default=2048),
+            tie_word_embeddings=_need_bool(d, "tie_word_embeddings", False),
+            attention_bias=_need_bool(d, "attention_bias", False),
+            mlp_bias=_need_bool(d, "mlp_bias", False),
+            hidden_act="silu",
+            bos_token_id=bos,
+            eos_token_ids=_token_ids(d, "eos_token_id"),
+        )
+        if cfg.mlp_bias:
+            raise ConfigError("config.json: mlp_bias true is not supported")
+        return cfg
+
+    @classmethod
+    def from_folder(cls, folder: str) -> "LlamaConfig":
+        return cls.from_dict(read_config_json(folder))
+
+    def to_dict(self) -> Dict[str, Any]:
+        """The config.json that reads back as this configuration."""
+        d: Dict[str, Any] = {
+            "architectures": [self.architecture],
+            "model_type": "llama",
+            "hidden_size": self.hidden_size,
+            "intermediate_size": self.intermediate_size,
+            "num_hidden_layers": self.num_hidden_layers,
+            "num_attention_heads": self.num_attention_heads,
+            "num_key_value_heads": self.num_key_value_heads,
+            "head_dim": self.head_dim,
+            "vocab_size": self.vocab_size,
+            "rms_norm_eps": self.rms_norm_eps,
+            "rope_theta": self.rope_theta,
+            "rope_scaling": self.rope_scaling.to_dict() if self.rope_scaling else None,
+            "max_position_embeddings": self.max_position_embeddings,
+            "tie_word_embeddings": self.tie_word_embeddings,
+            "attention_bias": self.attention_bias,
+            "mlp_bias": self.mlp_bias,
+            "hidden_act": self.hidden_act,
+        }
+        if self.bos_token_id is not None:
+            d["bos_token_id"] = self.bos_token_id
+        if self.eos_token_ids:
+            d["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
+        return d
+
+    # ----------------------------------------------------------- model structure
+    def model_spec(self) -> ModelSpec:
+        """Lay the architecture out as parts: L identical pre-norm blocks of
+        (RMSNorm, rotary grouped-query attention, RMSNorm, SwiGLU), run in order
+        (src/model.zig:543-789 is the reference's layer loop)."""
+        d = self.hidden_size
+        scaling = self.rope_scaling.to_dict() if self.rope_scaling else None
+        position = PositionSpec(kind="rope", rotary_dim=self.head_dim, theta=self.rope_theta,
+                                scaling=scaling, max_positions=self.max_position_embeddings)
+        layers = []
+        for i in range(self.num_hidden_layers):
+            layers.append(LayerSpec(
+                block="prenorm",
+                prefix=f"model.layers.{i}.",
+                mixer_norm=NormSpec("rmsnorm", d, self.rms_norm_eps),
+                mixer=MixerSpec(kind="attention", width=d, n_heads=self.num_attention_heads,
+                                n_kv_heads=self.num_key_value_heads, head_dim=self.head_dim,
+                                bias=self.attention_bias, out_bias=self.attention_bias,
+                                position=position),
+                ffn_norm=NormSpec("rmsnorm", d, self.rms_norm_eps),
+                ffn=FeedForwardSpec(kind="gated_mlp", width=d, intermediate=self.intermediate_size,
+                                    activation="silu", bias=False),
+                names={
+                    "mixer_norm.weight": "input_layernorm.weight",
+                    "mixer.q.weight": "self_attn.q_proj.weight",
+                    "mixer.k.weight": "self_attn.k_proj.weight",
+                    "mixer.v.weight": "self_attn.v_proj.weight",
+                    "mixer.o.weight": "self_attn.o_proj.weight",
+                    "mixer.q.bias": "self_attn.q_proj.bias",
+                    "mixer.k.bias": "self_attn.k_proj.bias",
+                    "mixer.v.bias": "self_attn.v_proj.bias",
+                    "mixer.o.bias": "self_attn.o_proj.bias",
+                    "ffn_norm.weight": "post_attention_layernorm.weight",
+                    "ffn.gate.weight": "mlp.gate_proj.weight",
+                    "ffn.up.weight": "mlp.up_proj.weight",
+                    "ffn.down.weight": "mlp.down_proj.weight",
+                },
+            ))
+        return ModelSpec(
+            architecture=self.architecture,
+            width=d,
+            vocab_size=self.vocab_size,
+            layers=tuple(layers),
+            schedule=tuple(range(self.num_hidden_layers)),
+            final_norm=NormSpec("rmsnorm", d, self.rms_norm_eps),
+            embedding_name="model.embed_tokens.weight",
+            final_norm_name="model.norm.weight",
+            head_name=None if self.tie_word_embeddings else "lm_head.weight",
+            embedding_scale=1.0,
+            max_positions=self.max_position_embeddings,
+            stop_token_ids=self.eos_token_ids,
+        )
+
+    # ------------------------------------------------------------------ counting
+    def parameter_count(self) -> int:
+        d, i, v = self.hidden_size, self.intermediate_size, self.vocab_size
+        q = self.num_attention_heads * self.head_dim
+        kv = self.num_key_value_heads * self.head_dim
+        per_layer = d * q + 2 * d * kv + q * d + 3 * d * i + 2 * d
+        if self.attention_bias:
+            per_layer += q + 2 * kv + d
+        total = self.num_hidden_layers * per_layer + v * d + d
+        if not self.tie_word_embeddings:
+            total += v * d
+        return total
+
+
+def read_config_json(folder: str) -> Dict[str, Any]:
+    path = os.path.join(folder, "config.json")
+    try:
+        with open(path, "r", encoding="utf-8") as f:
+            d = json.load(f)
+    except FileNotFoundError:
+        raise ConfigError(f"{path} does not exist") from None
+    except json.JSONDecodeError as e:
+        raise ConfigError(f"{path} is not valid JSON: {e}") from None
+    if not isinstance(d, dict):
+        raise ConfigError(f"{path} must hold a JSON object")
+    return d

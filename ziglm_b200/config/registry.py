@@ -1,0 +1,49 @@
+"""One registry from the architecture name in config.json to its configuration class.
+
+The reference's registry is a substring match from ``architectures[0]`` to an
+enum (src/safetensors.zig:517-532, src/types.zig:225-238) whose values the
+forward pass then branches on.  Here the name selects a configuration class;
+the class turns config.json into a typed configuration and that into a
+:class:`~ziglm_b200.config.spec.ModelSpec`, which is all the engine needs.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, Mapping
+
+from .llama import ConfigError, LlamaConfig, read_config_json
+from .spec import ModelSpec
+
+_ARCHITECTURES: Dict[str, Any] = {}
+
+
+def register_architecture(name: str, config_class: Any) -> None:
+    """``config_class`` needs ``from_dict(mapping)`` and, on its instances, ``model_spec()``."""
+    if name in _ARCHITECTURES and _ARCHITECTURES[name] is not config_class:
+        raise ValueError(f"architecture {name!r} is already registered")
+    _ARCHITECTURES[name] = config_class
+
+
+def unregister_architecture(name: str) -> None:
+    _ARCHITECTURES.pop(name, None)
+
+
+def registered_architectures():
+    return sorted(_ARCHITECTURES)
+
+
+def config_from_dict(d: Mapping[str, Any]):
+    arch = d.get("architectures") if isinstance(d, Mapping) else None
+    if not (isinstance(arch, (list, tuple)) and arch and isinstance(arch[0], str)):
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+    cls = _ARCHITECTURES.get(arch[0])
+    if cls is None:
+        raise ConfigError(
+            f"architecture {arch[0]!r} is not registered (known: {', '.join(registered_architectures())})")
+    return cls.from_dict(d)
+
+
+def config_from_folder(folder: str):
+    return config_from_dict(read_config_json(folder))
+
+
+register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)

@@ -1,0 +1,257 @@
+// Rotary positions, cache writes and attention over the paged cache: the plain
+// kernels that take every head size (a multiple of 8), every number of heads
+// and groups, both storage types, prompts, continued prompts and single decoded
+// tokens alike.  They are the whole 32-bit path and the fallback of the bf16
+// path for head sizes the tensor-core kernels do not cover.
+//
+// Formulas, as the reference computes them:
+//   RoPE     pairs (i, i+rot/2) inside a head: theta = pos*inv_freq[i],
+//            h[i]       = a*cos(theta) - b*sin(theta)
+//            h[i+rot/2] = a*sin(theta) + b*cos(theta)
+//            (src/model.zig:569-597,642-653; src/cuda_bridge.cu:2070-2108)
+//            inv_freq comes from a table built once from the configuration (the
+//            reference recomputes 1/powf(base, 2i/rot) per thread and ignores the
+//            configured base, src/model.zig:405-413).
+//   cache    keys are stored rotated (src/model.zig:655, src/kv_cache.zig:63-85)
+//   scores   kvh = h / (n_heads/n_kv_heads); s_t = (q_h . K[t,kvh]) * scale
+//            (src/model.zig:554,659-678)
+//   mask     a token at position p sees keys [start, p], start = 0 or
+//            p-window+1 (src/model.zig:660-661); nothing is materialised
+//   softmax  m = max s, e = exp(s-m), p = e/sum e in float (src/math.zig:1088-1106)
+//   values   o_h = sum_t p_t V[t,kvh,:] (src/model.zig:683-700)
+//
+// Cache layout: pages of `page_size` positions.  Page p of one layer holds
+// [n_kv_heads][page_size][head_dim] for keys and the same for values.  A step
+// gives each of its sequences a row of page numbers (`block_table`), so position
+// t of sequence b lives in page block_table[b*bt_stride + t/page_size], row
+// t%page_size.
+#include "common.cuh"
+
+namespace zlm {
+
+// ------------------------------------------------------- rope + cache write
+// grid (T, n_heads + 2*n_kv_heads); a thread per rotated pair, then per copied element
+// qkv row layout: [q: n_heads*hd | k: n_kv*hd | v: n_kv*hd]
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
+                                  const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                  const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                  int bt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size,
+                                  long page_stride) {
+    const int t = blockIdx.x;
+    const int head = blockIdx.y;
+    const int pos = positions[t];
+    T* row = qkv + (long)t * row_stride + (long)head * hd;
+    const bool is_q = head < n_heads;
+    const bool is_k = !is_q && head < n_heads + n_kv;
+    T* dst = nullptr;
+    if (!is_q && k_pages != nullptr) {
+        const int kvh = is_k ? head - n_heads : head - n_heads - n_kv;
+        const int b = seq_of_token[t];
+        const int page = block_table[(long)b * bt_stride + pos / page_size];
+        T* base = is_k ? k_pages : v_pages;
+        dst = base + (long)page * page_stride + ((long)kvh * page_size + pos % page_size) * hd;
+    }
+    const int half = rot / 2;
+    const bool rotate = (is_q || is_k) && inv_freq != nullptr;
+    if (rotate) {
+        // one thread per pair: both members are read before either is written
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float a = to_float(row[i]);
+            const float b2 = to_float(row[i + half]);
+            const float theta = (float)pos * inv_freq[i];
+            float s, c;
+            sincosf(theta, &s, &c);
+            const T lo = from_float<T>(a * c - b2 * s);
+            const T hi = from_float<T>(a * s + b2 * c);
+            row[i] = lo;
+            row[i + half] = hi;
+            if (dst) { dst[i] = lo; dst[i + half] = hi; }
+        }
+        if (dst)
+            for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = row[i];
+    } else if (dst) {
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = row[i];
+    }
+}
+
+// ------------------------------------------------------------ attention
+// grid (T, n_heads); 128 threads.  Warp w takes the key blocks w, w+4, ... of 32
+// keys; lane j scores key j of the block, then the lanes split the head's
+// dimensions for the weighted sum of values.  The four partial results are
+// merged in warp order, so the result depends only on (start, pos).
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_MAX_HD = 256;
+
+template <typename T, int VEC>
+__device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int hd);
+
+template <>
+__device__ __forceinline__ float dot_row<float, 4>(const float* __restrict__ q, const float* __restrict__ k, int hd) {
+    float acc = 0.f;
+    for (int d = 0; d < hd; d += 4) {
+        const float4 kv = *reinterpret_cast<const float4*>(k + d);
+        acc = fmaf(q[d], kv.x, acc);
+        acc = fmaf(q[d + 1], kv.y, acc);
+        acc = fmaf(q[d + 2], kv.z, acc);
+        acc = fmaf(q[d + 3], kv.w, acc);
+    }
+    return acc;
+}
+
+template <>
+__device__ __forceinline__ float dot_row<__nv_bfloat16, 8>(const float* __restrict__ q,
+                                                           const __nv_bfloat16* __restrict__ k, int hd) {
+    float acc = 0.f;
+    for (int d = 0; d < hd; d += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(k + d);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(p[i]);
+            acc = fmaf(q[d + 2 * i], f.x, acc);
+            acc = fmaf(q[d + 2 * i + 1], f.y, acc);
+        }
+    }
+    return acc;
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restrict__ out, int n_heads, int n_kv,
+                         int hd, float scale, int window, const int* __restrict__ positions,
+                         const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int bt_stride,
+                         const T* __restrict__ k_pages, const T* __restrict__ v_pages, int page_size,
+                         long page_stride) {
+    __shared__ float q_s[ATT_MAX_HD];
+    __shared__ float acc_s[ATT_WARPS][ATT_MAX_HD];
+    __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
+
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = positions[t];
+    const int b = seq_of_token[t];
+    const int kvh = h / (n_heads / n_kv);
+    const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int* bt = block_table + (long)b * bt_stride;
+
+    for (int i = threadIdx.x; i < hd; i += blockDim.x) q_s[i] = to_float(q[(long)t * q_row_stride + (long)h * hd + i]);
+    __syncthreads();
+
+    constexpr int NREG = ATT_MAX_HD / 32;
+    float acc[NREG];
+#pragma unroll
+    for (int i = 0; i < NREG; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    const int n_keys = pos - start + 1;
+    const int n_blocks = (n_keys + 31) / 32;
+    for (int kb = warp; kb < n_blocks; kb += ATT_WARPS) {
+        const int j = start + kb * 32 + lane;
+        const bool valid = j <= pos;
+        float s = -INFINITY;
+        long row_off = 0;
+        if (valid) {
+            const int page = bt[j / page_size];
+            row_off = (long)page * page_stride + ((long)kvh * page_size + j % page_size) * hd;
+            s = dot_row<T, VEC>(q_s, k_pages + row_off, hd) * scale;
+        }
+        const float m_new = fmaxf(m, warp_max(s));       // lane 0 of the block is always valid
+        const float corr = expf(m - m_new);               // exp(-inf) = 0 on the first block
+        const float p = valid ? expf(s - m_new) : 0.f;
+        l = l * corr + warp_sum(p);
+        m = m_new;
+#pragma unroll
+        for (int i = 0; i < NREG; ++i) acc[i] *= corr;
+        const int n_valid = min(32, pos - (start + kb * 32) + 1);
+        for (int jj = 0; jj < n_valid; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const long voff = __shfl_sync(0xffffffffu, row_off, jj);
+            const T* vrow = v_pages + voff;
+#pragma unroll
+            for (int i = 0; i < NREG; ++i) {
+                const int d = lane + 32 * i;
+                if (d < hd) acc[i] = fmaf(pj, to_float(vrow[d]), acc[i]);
+            }
+        }
+    }
+
+    if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < NREG; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) acc_s[warp][d] = acc[i];
+    }
+    __syncthreads();
+
+    float big = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) big = fmaxf(big, m_s[w]);
+    float wgt[ATT_WARPS];
+    float denom = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+        wgt[w] = m_s[w] == -INFINITY ? 0.f : expf(m_s[w] - big);
+        denom += l_s[w] * wgt[w];
+    }
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) o += acc_s[w][d] * wgt[w];
+        out[((long)t * n_heads + h) * hd + d] = from_float<T>(o / denom);
+    }
+}
+
+}  // namespace zlm
+
+using namespace zlm;
+
+// Rotates q and k in place inside qkv and copies k (rotated) and v into the cache.
+// inv_freq == nullptr: no rotation.  k_pages == nullptr: nothing is stored (a layer
+// that reads another layer's cache).
+ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int n_heads, int n_kv, int hd, int rot,
+                              const float* inv_freq, const int* positions, const int* seq_of_token,
+                              const int* block_table, int bt_stride, void* k_pages, void* v_pages, int page_size,
+                              long page_stride, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hd <= 0 || rot < 0 || rot > hd || (rot & 1) || n_heads <= 0 || n_kv < 0 || page_size <= 0)
+        return ZLM_ERR_BAD_ARG;
+    int threads = 32;
+    while (threads < hd && threads < 256) threads <<= 1;
+    dim3 grid(T, n_heads + 2 * n_kv);
+    if (dtype == ZLM_F32)
+        rope_store_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, row_stride, n_heads, n_kv, hd, rot,
+                                                               inv_freq, positions, seq_of_token, block_table,
+                                                               bt_stride, (float*)k_pages, (float*)v_pages,
+                                                               page_size, page_stride);
+    else if (dtype == ZLM_BF16)
+        rope_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+            (__nv_bfloat16*)qkv, row_stride, n_heads, n_kv, hd, rot, inv_freq, positions, seq_of_token, block_table,
+            bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, page_stride);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return launch_status();
+}
+
+ZLM_EXPORT int zlm_attention_general(const void* q, long q_row_stride, void* out, int dtype, int T, int n_heads,
+                                     int n_kv, int hd, float scale, int window, const int* positions,
+                                     const int* seq_of_token, const int* block_table, int bt_stride,
+                                     const void* k_pages, const void* v_pages, int page_size, long page_stride,
+                                     cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0) return ZLM_ERR_BAD_ARG;
+    if (hd <= 0 || hd > ATT_MAX_HD || hd % 8) return ZLM_ERR_UNSUPPORTED;
+    dim3 grid(T, n_heads);
+    if (dtype == ZLM_F32)
+        attention_general_kernel<float, 4><<<grid, ATT_WARPS * 32, 0, stream>>>(
+            (const float*)q, q_row_stride, (float*)out, n_heads, n_kv, hd, scale, window, positions, seq_of_token,
+            block_table, bt_stride, (const float*)k_pages, (const float*)v_pages, page_size, page_stride);
+    else if (dtype == ZLM_BF16)
+        attention_general_kernel<__nv_bfloat16, 8><<<grid, ATT_WARPS * 32, 0, stream>>>(
+            (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, n_heads, n_kv, hd, scale, window, positions,
+            seq_of_token, block_table, bt_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+            page_size, page_stride);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return launch_status();
+}

@@ -1,0 +1,151 @@
+// Embedding gather, RMSNorm (with optional row gather) and the gated activation.
+//
+// Formulas follow the reference:
+//   embedding  x = W_e[token] widened to float, times a scale that is 1 for this
+//              architecture                      (src/model.zig:495-503)
+//   RMSNorm    ss = sum x_i^2, inv = 1/sqrt(ss/n + eps), y_i = (x_i*inv)*w_i
+//              (src/math.zig:850-945; GPU twin src/cuda_bridge.cu:1475-1534)
+//   SwiGLU     act_j = silu(g_j)*u_j, silu(z) = z/(1+exp(-z))
+//              (src/math.zig:1108-1117, src/cuda_bridge.cu:2271-2285)
+// The residual stream is float in both precisions, so the norm always reads
+// float and writes the storage type of the next matrix product.
+#include "common.cuh"
+
+namespace zlm {
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int d, float scale) {
+    const int t = blockIdx.x;
+    const long row = (long)tokens[t] * d;
+    float* o = out + (long)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_float(table[row + i]) * scale;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per output row.  rows == nullptr: row r of the input; otherwise row
+// rows[r] (this is how the final norm runs on the wanted positions only).
+template <typename TW, typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                               const int* __restrict__ rows, int d, float eps, float weight_offset) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (long)(rows ? rows[r] : r) * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (long)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        o[i] = from_float<TO>((xr[i] * inv) * (to_float(w[i]) + weight_offset));
+}
+
+// --------------------------------------------------------- gated activation
+// gu is [T, 2*I]: gate in columns [0, I), up in columns [I, 2I).
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, long total, int I, int kind) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long t = idx / I;
+    const int j = (int)(idx - t * I);
+    const float g = to_float(gu[t * 2 * I + j]);
+    const float u = to_float(gu[t * 2 * I + I + j]);
+    float a;
+    if (kind == 0) {
+        a = g / (1.0f + expf(-g));                         // silu
+    } else {
+        const float c = 0.7978845608028654f;               // gelu (tanh form)
+        a = 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
+    }
+    out[idx] = from_float<T>(a * u);
+}
+
+// y += x (float), used by parts that cannot fold their residual sum into a product
+__global__ void add_kernel(float* __restrict__ y, const float* __restrict__ x, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] += x[i];
+}
+
+template <typename TI, typename TO>
+__global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_float<TO>(to_float(in[i]));
+}
+
+static int norm_threads(int d) {
+    int t = 32;
+    while (t < 512 && t * 4 < d) t <<= 1;
+    return t;
+}
+
+}  // namespace zlm
+
+using namespace zlm;
+
+ZLM_EXPORT int zlm_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int d,
+                         float scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0) return ZLM_ERR_BAD_ARG;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == ZLM_F32)
+        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, d, scale);
+    else if (table_dtype == ZLM_BF16)
+        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, d, scale);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return launch_status();
+}
+
+ZLM_EXPORT int zlm_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype, const int* rows,
+                           int n_rows, int d, float eps, float weight_offset, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) return ZLM_ERR_BAD_ARG;
+    const int threads = norm_threads(d);
+#define ZLM_NORM(TW, TO)                                                                                      \
+    rmsnorm_kernel<TW, TO><<<n_rows, threads, 0, stream>>>(x, (const TW*)w, (TO*)out, rows, d, eps, weight_offset)
+    if (w_dtype == ZLM_F32 && out_dtype == ZLM_F32) ZLM_NORM(float, float);
+    else if (w_dtype == ZLM_F32 && out_dtype == ZLM_BF16) ZLM_NORM(float, __nv_bfloat16);
+    else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_F32) ZLM_NORM(__nv_bfloat16, float);
+    else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_BF16) ZLM_NORM(__nv_bfloat16, __nv_bfloat16);
+    else return ZLM_ERR_UNSUPPORTED;
+#undef ZLM_NORM
+    return launch_status();
+}
+
+ZLM_EXPORT int zlm_gated_act(const void* gu, void* out, int dtype, int T, int I, int kind, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (I <= 0 || (kind != 0 && kind != 1)) return ZLM_ERR_BAD_ARG;
+    const long total = (long)T * I;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (dtype == ZLM_F32)
+        gated_act_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, I, kind);
+    else if (dtype == ZLM_BF16)
+        gated_act_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu,
+                                                                         (__nv_bfloat16*)out, total, I, kind);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return launch_status();
+}
+
+ZLM_EXPORT int zlm_add(float* y, const float* x, long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(y, x, n);
+    return launch_status();
+}
+
+ZLM_EXPORT int zlm_convert(const void* in, int in_dtype, void* out, int out_dtype, long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (in_dtype == ZLM_F32 && out_dtype == ZLM_BF16)
+        convert_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, n);
+    else if (in_dtype == ZLM_BF16 && out_dtype == ZLM_F32)
+        convert_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, n);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return launch_status();
+}

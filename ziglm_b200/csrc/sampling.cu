@@ -1,0 +1,367 @@
+// Sampling on the device: argmax, and the reference's sampler chain.
+//
+// The reference samples on the host (src/sampler.zig:31-157): optional
+// repetition/presence penalties over the last ids, logits * (1/T), softmax, sort by
+// probability, keep top_k, cut below min_p * p_max (at least one stays), cut once
+// the running probability reaches top_p, then draw r = u * sum(kept) and take the
+// first kept candidate whose running sum reaches r.  Greedy is the plain argmax
+// (src/sampler.zig:159-170; device twin src/cuda_bridge.cu:2946-3062).  Here one
+// block of 1024 threads handles one row of logits:
+//   * argmax scans every id (the reference's CPU argmax skips id 0, its GPU one does
+//     not); the lowest id wins ties.
+//   * with top_k in [1, 1024] the k best candidates are selected exactly (radix select
+//     on the scaled logits, ties to the lower id), sorted by (probability descending,
+//     id ascending) and cut and drawn from in that order by one thread, in the same
+//     float operations as the plain statement of the chain.
+//   * with top_k == 0 the candidates stay in id order: min_p is a threshold, the
+//     draw is a running sum over ids.  top_p < 1 needs top_k and is refused without.
+// The uniform number of a draw is a pure function of (seed, counter) of the row, so
+// a sequence draws the same whatever else is in its batch.
+#include "common.cuh"
+
+namespace zlm {
+
+constexpr int SAMPLE_THREADS = 1024;
+constexpr int MAX_TOP_K = 1024;
+
+// splitmix64, the integer hash behind the per-row uniform draw
+__host__ __device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__device__ __forceinline__ float uniform01(unsigned long long seed, unsigned long long counter) {
+    const unsigned long long h = mix64(seed ^ mix64(counter));
+    return (float)(h >> 40) * (1.0f / 16777216.0f);   // 24 bits, [0, 1)
+}
+
+// order-preserving map from float to unsigned
+__device__ __forceinline__ unsigned orderable(float f) {
+    const unsigned u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// exclusive prefix sum of one int per thread over the block (blockDim.x == 1024)
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_totals, int* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    __syncthreads();
+    if (lane == 31) warp_totals[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_totals[lane];
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        warp_totals[lane] = winc - w;
+        if (lane == 31) *total = winc;
+    }
+    __syncthreads();
+    return warp_totals[warp] + inc - v;
+}
+
+__device__ __forceinline__ float block_exclusive_scan_f(float v, float* warp_totals, float* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    __syncthreads();
+    if (lane == 31) warp_totals[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        float w = warp_totals[lane];
+        float winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        warp_totals[lane] = winc - w;
+        if (lane == 31) *total = winc;
+    }
+    __syncthreads();
+    return warp_totals[warp] + inc - v;
+}
+
+// ------------------------------------------------------------------- argmax
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int V, long row_stride, int* __restrict__ out) {
+    __shared__ float vals[32];
+    __shared__ int idxs[32];
+    const float* row = logits + (long)blockIdx.x * row_stride;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || bi == 0x7fffffff) { best = v; bi = i; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { vals[warp] = best; idxs[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < (blockDim.x >> 5) ? vals[lane] : -INFINITY;
+        bi = lane < (blockDim.x >> 5) ? idxs[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = bi;
+    }
+}
+
+// ------------------------------------------------------------------- sample
+struct SampleArgs {
+    float inv_temperature;
+    int top_k;
+    float top_p;
+    float min_p;
+    float repetition_penalty;
+    float presence_penalty;
+    int window;           // ids of history per row (0: none); history is [rows, window], -1 = empty
+};
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(float* __restrict__ logits, int V, long row_stride, SampleArgs a, const int* __restrict__ history,
+              const long long* __restrict__ rng, int* __restrict__ out) {
+    __shared__ float fscratch[33];
+    __shared__ int iscratch[32];
+    __shared__ int itotal;
+    __shared__ float ftotal;
+    __shared__ int hist[256];
+    __shared__ unsigned prefix_s;
+    __shared__ int remaining_s;
+    __shared__ float cand_z[MAX_TOP_K];
+    __shared__ int cand_id[MAX_TOP_K];
+    __shared__ int n_cand;
+
+    const int tid = threadIdx.x;
+    float* row = logits + (long)blockIdx.x * row_stride;
+
+    // 0. penalties, once per occurrence in the window, in window order
+    if (a.window > 0 && (a.repetition_penalty != 1.0f || a.presence_penalty != 0.0f)) {
+        const int* h = history + (long)blockIdx.x * a.window;
+        if (tid < a.window) {
+            const int tok = h[tid];
+            bool first = tok >= 0 && tok < V;
+            for (int j = 0; j < tid && first; ++j) first = h[j] != tok;
+            if (first) {
+                float l = row[tok];
+                for (int j = tid; j < a.window; ++j) {
+                    if (h[j] != tok) continue;
+                    l = l > 0.f ? l / a.repetition_penalty : l * a.repetition_penalty;
+                    l -= a.presence_penalty;
+                }
+                row[tok] = l;
+            }
+        }
+        __syncthreads();
+    }
+
+    // 1. scaled logits, their max, the softmax denominator
+    float m = -INFINITY;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) m = fmaxf(m, row[i] * a.inv_temperature);
+    m = block_max(m, fscratch);
+    // contiguous chunks from here on, so that running sums follow the id order
+    const int chunk = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
+    float part = 0.f;
+    for (int i = lo; i < hi; ++i) part += expf(row[i] * a.inv_temperature - m);
+    float denom;
+    block_exclusive_scan_f(part, fscratch, &ftotal);
+    denom = ftotal;
+    __syncthreads();
+
+    const float u = uniform01((unsigned long long)rng[2 * blockIdx.x], (unsigned long long)rng[2 * blockIdx.x + 1]);
+
+    if (a.top_k <= 0) {
+        // candidates in id order; min_p is a threshold on the probability
+        const float thresh = a.min_p > 0.f ? (1.0f / denom) * a.min_p : -1.f;
+        float kept = 0.f;
+        for (int i = lo; i < hi; ++i) {
+            const float p = expf(row[i] * a.inv_temperature - m) / denom;
+            if (p >= thresh) kept += p;
+        }
+        const float before = block_exclusive_scan_f(kept, fscratch, &ftotal);
+        const float r = u * ftotal;
+        // the first id whose running sum reaches r: the thread whose chunk crosses r walks it
+        if (tid == 0) { itotal = -1; n_cand = -1; }
+        __syncthreads();
+        int found = -1, last_kept = -1;
+        float run = before;
+        for (int i = lo; i < hi; ++i) {
+            const float p = expf(row[i] * a.inv_temperature - m) / denom;
+            if (p >= thresh) {
+                last_kept = i;
+                run += p;
+                if (found < 0 && r <= run) found = i;
+            }
+        }
+        if (found >= 0) atomicMin((unsigned*)&itotal, (unsigned)found);   // -1 is the largest unsigned
+        if (last_kept >= 0) atomicMax(&n_cand, last_kept);
+        __syncthreads();
+        if (tid == 0) out[blockIdx.x] = itotal >= 0 ? itotal : max(n_cand, 0);
+        return;
+    }
+
+    // 2. exact top-k: radix select of the k-th largest scaled logit
+    const int k = min(min(a.top_k, MAX_TOP_K), V);
+    if (tid == 0) { prefix_s = 0u; remaining_s = k; }
+    __syncthreads();
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const unsigned prefix = prefix_s;
+        const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int i = tid; i < V; i += SAMPLE_THREADS) {
+            const unsigned key = orderable(row[i] * a.inv_temperature);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int rem = remaining_s;
+            int b = 255;
+            for (; b > 0; --b) {
+                if (hist[b] >= rem) break;
+                rem -= hist[b];
+            }
+            prefix_s = prefix | ((unsigned)b << shift);
+            remaining_s = rem;
+        }
+        __syncthreads();
+    }
+    const unsigned kth = prefix_s;          // key of the k-th largest; remaining_s ties of it are kept
+    const int ties_needed = remaining_s;
+    if (tid == 0) n_cand = 0;
+    __syncthreads();
+    int my_ties = 0;
+    for (int i = lo; i < hi; ++i) {
+        const float z = row[i] * a.inv_temperature;
+        const unsigned key = orderable(z);
+        if (key > kth) {
+            const int slot = atomicAdd(&n_cand, 1);
+            cand_z[slot] = z;
+            cand_id[slot] = i;
+        } else if (key == kth) {
+            ++my_ties;
+        }
+    }
+    const int tie_rank = block_exclusive_scan(my_ties, iscratch, &itotal);
+    __syncthreads();
+    const int n_above = n_cand;
+    {
+        int rank = tie_rank;
+        for (int i = lo; i < hi && rank < ties_needed; ++i) {
+            const float z = row[i] * a.inv_temperature;
+            if (orderable(z) == kth) {
+                cand_z[n_above + rank] = z;
+                cand_id[n_above + rank] = i;
+                ++rank;
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = k + tid; i < MAX_TOP_K; i += SAMPLE_THREADS) { cand_z[i] = -INFINITY; cand_id[i] = 0x7fffffff; }
+    __syncthreads();
+
+    // 3. bitonic sort by (z descending, id ascending)
+    for (int size = 2; size <= MAX_TOP_K; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const int i = tid;
+            const int j = i ^ stride;
+            if (j > i) {
+                const bool up = (i & size) == 0;
+                const float zi = cand_z[i], zj = cand_z[j];
+                const int ii = cand_id[i], ij = cand_id[j];
+                const bool i_first = zi > zj || (zi == zj && ii < ij);   // i belongs before j
+                if (i_first != up) {
+                    cand_z[i] = zj; cand_z[j] = zi;
+                    cand_id[i] = ij; cand_id[j] = ii;
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // 4. cut and draw, one thread, in the order and the float operations of the chain
+    if (tid == 0) {
+        int n = k;
+        const float p0 = expf(cand_z[0] - m) / denom;
+        if (a.min_p > 0.f) {
+            const float thresh = p0 * a.min_p;
+            for (int i = 0; i < n; ++i) {
+                if (expf(cand_z[i] - m) / denom < thresh) { n = max(1, i); break; }
+            }
+        }
+        if (a.top_p < 1.0f) {
+            float cum = 0.f;
+            for (int i = 0; i < n; ++i) {
+                cum += expf(cand_z[i] - m) / denom;
+                if (cum >= a.top_p) { n = i + 1; break; }
+            }
+        }
+        float total = 0.f;
+        for (int i = 0; i < n; ++i) total += expf(cand_z[i] - m) / denom;
+        const float r = u * total;
+        float run = 0.f;
+        int pick = cand_id[0];
+        for (int i = 0; i < n; ++i) {
+            run += expf(cand_z[i] - m) / denom;
+            if (r <= run) { pick = cand_id[i]; break; }
+        }
+        out[blockIdx.x] = pick;
+    }
+}
+
+}  // namespace zlm
+
+using namespace zlm;
+
+ZLM_EXPORT int zlm_argmax(const float* logits, int rows, int V, long row_stride, int* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (V <= 0 || row_stride < V) return ZLM_ERR_BAD_ARG;
+    argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, V, row_stride, out);
+    return launch_status();
+}
+
+// logits are modified in place when penalties are on.  rng: [rows][2] = (seed, counter).
+ZLM_EXPORT int zlm_sample(float* logits, int rows, int V, long row_stride, float temperature, int top_k, float top_p,
+                          float min_p, float repetition_penalty, float presence_penalty, const int* history,
+                          int window, const long long* rng, int* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (V <= 0 || row_stride < V || !(temperature > 0.f) || top_k < 0 || window < 0 || window > SAMPLE_THREADS)
+        return ZLM_ERR_BAD_ARG;
+    if (top_k > MAX_TOP_K) return ZLM_ERR_UNSUPPORTED;
+    if (top_k == 0 && top_p < 1.0f) return ZLM_ERR_UNSUPPORTED;
+    SampleArgs a;
+    a.inv_temperature = 1.0f / temperature;
+    a.top_k = top_k;
+    a.top_p = top_p;
+    a.min_p = min_p;
+    a.repetition_penalty = repetition_penalty;
+    a.presence_penalty = presence_penalty;
+    a.window = history ? window : 0;
+    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, V, row_stride, a, history, rng, out);
+    return launch_status();
+}

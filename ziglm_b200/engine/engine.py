@@ -1,0 +1,258 @@
+"""The engine: a model on one GPU, its cache, and the one step function everything goes through.
+
+Names follow the reference's library surface (src/root.zig:22-35): ``Engine``
+with ``load`` (src/engine.zig:64), ``prefill`` (321), ``decode`` (345),
+``generate`` (382) and ``reset`` (287); ``EngineOptions`` (src/engine.zig:32-37).
+The reference serves one sequence; here ``step`` takes a batch of sequences that
+either all start at their first token or all go on, each with its own length,
+runs exactly the tokens it is given from the cache earlier steps left, and
+returns the logits at the wanted places.  ``prefill``/``decode``/``reset`` are the
+reference's single-sequence calls expressed through ``step``.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import kernels
+from ..cache import CacheStorage, PAGE_SIZE
+from ..config import config_from_dict, config_from_folder
+from ..weights import load_tensors, random_tensors
+from .batch import BatchLayout, StepContext, pack_batch, views
+from .model import Model, declare_parameters
+from .workspace import Workspace
+
+
+class StepError(ValueError):
+    """The step was asked for something it cannot run (empty sequence, unknown token, ...)."""
+
+
+@dataclass
+class EngineOptions:
+    """Options of ``Engine.load``; the first four are the reference's (src/engine.zig:32-37).
+
+    num_threads  accepted and ignored (the reference's CPU worker count).
+    max_seq_len  positions one sequence may hold; default min(max_position_embeddings, 4096),
+                 the reference's choice (src/engine.zig:207).
+    seed         seed of sampling (and of random weights when there is no folder).
+    use_gpu      must stay true: there is no CPU path.
+    dtype        "bfloat16" (the kernels and precisions of serving) or "float32" (everything in true 32-bit).
+    max_tokens   positions the cache holds for all live sequences together, each sequence rounded up to
+                 whole pages of 64; default max_batch * max_seq_len.
+    max_batch    most sequences alive at once (slots).
+    device       CUDA device.
+    """
+    num_threads: Optional[int] = None
+    max_seq_len: Optional[int] = None
+    seed: int = 42
+    use_gpu: bool = True
+    dtype: str = "bfloat16"
+    max_tokens: Optional[int] = None
+    max_batch: int = 8
+    device: str = "cuda:0"
+    use_graphs: bool = True
+
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
+           "fp32": torch.float32}
+
+
+def _require_cuda(device: str) -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("ziglm_b200 needs a CUDA device (sm_100a); there is no CPU path")
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError(f"ziglm_b200 runs on CUDA devices only, not on {device!r}")
+    return dev
+
+
+class Engine:
+    def __init__(self, config, model: Model, options: EngineOptions):
+        self.config = config
+        self.model = model
+        self.options = options
+        self.spec = model.spec
+        self.device = model.device
+        self.dtype = model.dtype
+        limit = self.spec.max_positions or 4096
+        self.max_seq_len = int(options.max_seq_len) if options.max_seq_len else min(limit, 4096)
+        if self.spec.max_positions and self.max_seq_len > self.spec.max_positions:
+            raise ValueError(f"max_seq_len {self.max_seq_len} exceeds the model's max_position_embeddings "
+                             f"{self.spec.max_positions}")
+        max_tokens = options.max_tokens or options.max_batch * (-(-self.max_seq_len // PAGE_SIZE) * PAGE_SIZE)
+        n_slots = max(1, min(options.max_batch, -(-max_tokens // PAGE_SIZE)))
+        kv, reads, state = model.cache_plan()
+        self.cache = CacheStorage(kv, reads, state, max_tokens, n_slots, self.max_seq_len, self.dtype, self.device)
+        self.ws = Workspace(self.device)
+        self._host = [None, None]
+        self._host_events = [None, None]
+        self._dev: Optional[torch.Tensor] = None
+        self._flip = 0
+        self._graphs: Dict[Tuple[int, int], object] = {}
+        self._default_slot: Optional[int] = None
+        kernels.require(model.kernel_libraries())
+
+    # ---------------------------------------------------------------- creation
+    @classmethod
+    def load(cls, model_path: str, options: Optional[EngineOptions] = None) -> "Engine":
+        """Load a model folder (config.json + model.safetensors); the class of model is chosen by config.json."""
+        options = options or EngineOptions()
+        if not options.use_gpu:
+            raise RuntimeError("use_gpu=False: there is no CPU path in this library")
+        device = _require_cuda(options.device)
+        dtype = _DTYPES[options.dtype]
+        if os.path.isfile(model_path):
+            model_path = os.path.dirname(os.path.abspath(model_path))
+        config = config_from_folder(model_path)
+        spec = config.model_spec()
+        declared = declare_parameters(spec)
+        torch.cuda.set_device(device)
+        tensors = load_tensors(model_path, declared, dtype, device)
+        model = Model(spec, dtype, device)
+        model.bind(tensors)
+        return cls(config, model, options)
+
+    @classmethod
+    def from_config(cls, config, options: Optional[EngineOptions] = None, std: float = 0.02,
+                    norm_jitter: float = 0.0) -> "Engine":
+        """A model with random weights made on the device from ``options.seed`` (no files)."""
+        options = options or EngineOptions()
+        device = _require_cuda(options.device)
+        dtype = _DTYPES[options.dtype]
+        if isinstance(config, dict):
+            config = config_from_dict(config)
+        spec = config.model_spec()
+        declared = declare_parameters(spec)
+        torch.cuda.set_device(device)
+        tensors = dict(random_tensors(declared, options.seed, dtype, device, std, norm_jitter))
+        model = Model(spec, dtype, device)
+        model.bind(tensors)
+        return cls(config, model, options)
+
+    # ------------------------------------------------------------------- slots
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.slots.length_of(slot)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    # -------------------------------------------------------------------- step
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """Run one step.
+
+        entries  (slot, tokens) per sequence: the next tokens of that sequence, at least one.
+        want     per sequence, the places among its tokens whose logits are wanted
+                 (default: the last token of each).
+        Returns float32 logits [n_wanted, vocab] on the device, in the order of the entries
+        and of ``want``, or None if nothing is wanted.  The tensor is scratch of the engine:
+        it is overwritten by the next step.
+        """
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        slots = [int(s) for s, _ in entries]
+        new_tokens = [list(t) for _, t in entries]
+        if len(set(slots)) != len(slots):
+            raise StepError("a slot appears twice in one step")
+        V = self.spec.vocab_size
+        for s, toks in zip(slots, new_tokens):
+            if not toks:
+                raise StepError(f"slot {s}: a sequence must bring at least one token")
+            for t in toks:
+                if not (0 <= int(t) < V):
+                    raise StepError(f"slot {s}: token {t} is outside the vocabulary of {V}")
+        past = [self.cache.slots.length_of(s) for s in slots]
+        if want is None:
+            want = [[len(t) - 1] for t in new_tokens]
+        if len(want) != len(entries):
+            raise StepError("`want` needs one list per sequence")
+        want_rows: List[int] = []
+        start = 0
+        for toks, w in zip(new_tokens, want):
+            for i in w:
+                if not (0 <= int(i) < len(toks)):
+                    raise StepError(f"wanted place {i} is outside the {len(toks)} tokens of its sequence")
+                want_rows.append(start + int(i))
+            start += len(toks)
+
+        growth = {s: len(t) for s, t in zip(slots, new_tokens)}
+        self.cache.slots.reserve(growth)
+
+        T = start
+        B = len(slots)
+        single = all(len(t) == 1 for t in new_tokens)
+        max_total = max(p + len(t) for p, t in zip(past, new_tokens))
+        width = -(-max_total // self.cache.page_size)
+        widths = tuple(width for _ in self.cache.groups)
+        layout = BatchLayout(T, B, len(want_rows), widths)
+        tables = [self.cache.block_table_rows(g, slots, width) for g in range(len(self.cache.groups))]
+
+        host, dev = self._buffers(layout.total)
+        pack_batch(layout, host, slots, past, new_tokens, want_rows, tables)
+        dev[:layout.total].copy_(host[:layout.total], non_blocking=True)
+        self._host_events[self._flip].record()
+        v = views(layout, dev)
+        step = StepContext(
+            n_tokens=T, n_seqs=B, n_want=len(want_rows), tokens=v["tokens"], positions=v["positions"],
+            seq_of_token=v["seq_of_token"], cu_seqlens=v["cu_seqlens"], past_lens=v["past_lens"],
+            total_lens=v["total_lens"], slots=v["slots"], want_rows=v["want_rows"], block_tables=v["block_tables"],
+            single_token=single, max_new=max(len(t) for t in new_tokens), max_total=max_total, dtype=self.dtype,
+            device=self.device, ws=self.ws, host_past_lens=past, host_new_lens=[len(t) for t in new_tokens],
+            host_slots=slots)
+        step.io = [self.cache.io_for(place, step.block_tables) for place in range(len(self.spec.schedule))]
+        logits = self.model.forward(step)
+        self.cache.slots.advance(growth)
+        return logits
+
+    def _buffers(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """A pinned staging buffer that no copy in flight still reads, and the device buffer."""
+        self._flip ^= 1
+        i = self._flip
+        if self._host[i] is None or self._host[i].numel() < n:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            self._host[i] = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._host_events[i] = torch.cuda.Event()
+        else:
+            self._host_events[i].synchronize()
+        if self._dev is None or self._dev.numel() < n:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        return self._host[i], self._dev
+
+    # ---------------------------------------- the reference's single-sequence calls
+    def reset(self) -> None:
+        """Forget the sequence of ``prefill``/``decode`` (the reference rewinds its one cache, src/engine.zig:287)."""
+        if self._default_slot is not None:
+            self.free_slot(self._default_slot)
+            self._default_slot = None
+
+    def prefill(self, tokens: Sequence[int]) -> torch.Tensor:
+        """Run a whole prompt for the engine's own sequence; logits of its last token, float32 [vocab]."""
+        if len(tokens) == 0:
+            raise StepError("the prompt is empty")
+        if self._default_slot is None:
+            self._default_slot = self.alloc_slot()
+        return self.step([(self._default_slot, tokens)])[0]
+
+    def decode(self, token: int, pos: int) -> torch.Tensor:
+        """Run one more token of the engine's own sequence at position ``pos``; its logits."""
+        if self._default_slot is None:
+            self._default_slot = self.alloc_slot()
+        have = self.length(self._default_slot)
+        if pos != have:
+            raise StepError(f"decode at position {pos}, but the sequence holds {have} tokens")
+        return self.step([(self._default_slot, [int(token)])])[0]
+
+    def generate(self, prompts, options=None, callback=None):
+        from .generate import generate
+        return generate(self, prompts, options, callback)

@@ -1,0 +1,32 @@
+"""Scratch memory of a step: named device buffers that are kept and reused.
+
+Layers run one after another and ask for the same names, so a step's scratch is
+as large as its largest layer needs.  A buffer grows when a larger request
+comes; an engine that has captured CUDA graphs gives each graph a workspace of
+its own, so that growth elsewhere never moves memory a graph still points to.
+"""
+from __future__ import annotations
+
+from typing import Dict, Tuple
+
+import torch
+
+
+class Workspace:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._flat: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+
+    def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        flat = self._flat.get(key)
+        if flat is None or flat.numel() < n:
+            flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._flat[key] = flat
+        return flat[:n].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._flat.values())

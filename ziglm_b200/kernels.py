@@ -1,0 +1,322 @@
+"""Typed Python wrappers of the CUDA entry points in ``csrc/``.
+
+Every wrapper checks what the kernel cannot (device, dtype, contiguity, sizes it
+refuses), passes raw pointers and the current CUDA stream through the C ABI and
+raises :class:`KernelError` on a non-zero status.  There is no CPU path: a call
+with a tensor that is not on a CUDA device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import builder as _build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+_launches = 0   # kernels launched through these wrappers since the last reset
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or the launch failed."""
+
+
+def launches() -> int:
+    return _launches
+
+
+def reset_launches() -> None:
+    global _launches
+    _launches = 0
+
+
+def code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported by the kernels (float32 and bfloat16 are)") from None
+
+
+_PROTOTYPES = {
+    "elementwise": {
+        "zlm_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+        "zlm_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float,
+                        c_void_p],
+        "zlm_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "zlm_add": [c_void_p, c_void_p, c_long, c_void_p],
+        "zlm_convert": [c_void_p, c_int, c_void_p, c_int, c_long, c_void_p],
+    },
+    "gemm_generic": {
+        "zlm_gemm_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_long, c_long, c_long, c_void_p],
+    },
+    "attention": {
+        "zlm_rope_store": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                           c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
+        "zlm_attention_general": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
+    },
+    "sampling": {
+        "zlm_argmax": [c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
+        "zlm_sample": [c_void_p, c_int, c_int, c_long, c_float, c_int, c_float, c_float, c_float, c_float, c_void_p,
+                       c_int, c_void_p, c_void_p, c_void_p],
+    },
+}
+_functions = {}
+
+
+def _fn(library: str, name: str):
+    f = _functions.get(name)
+    if f is None:
+        lib = _build.load(library)
+        f = getattr(lib, name)
+        f.argtypes = _PROTOTYPES[library][name]
+        f.restype = c_int
+        _functions[name] = f
+    return f
+
+
+def require(libraries) -> None:
+    """Compile (if need be) and load the named kernel libraries, several at a time."""
+    _build.build(list(libraries))
+    for lib in libraries:
+        _build.load(lib)
+
+
+_STATUS = {-1: "bad argument", -2: "unsupported size or type", -3: "scratch memory too small"}
+
+
+def _check(status: int, what: str) -> None:
+    global _launches
+    if status == 0:
+        _launches += 1
+        return
+    if status < 0:
+        raise KernelError(f"{what}: {_STATUS.get(status, 'error %d' % status)}")
+    raise KernelError(f"{what}: CUDA error {status}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be on a CUDA device (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
+
+
+# ------------------------------------------------------------------ elementwise
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = float(table[tokens[t], :]) * scale;  out is float32 [T, d]."""
+    _cuda(table, "table"); _cuda(tokens, "tokens", torch.int32); _cuda(out, "out", torch.float32)
+    T, d = out.shape
+    if table.shape[1] != d or tokens.numel() < T:
+        raise KernelError("embed: shapes do not match")
+    _check(_fn("elementwise", "zlm_embed")(table.data_ptr(), code(table.dtype), tokens.data_ptr(), out.data_ptr(),
+                                           T, d, scale, _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None, weight_offset: float = 0.0) -> None:
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * (weight + weight_offset); x is float32."""
+    _cuda(x, "x", torch.float32); _cuda(weight, "weight"); _cuda(out, "out")
+    n, d = out.shape
+    if x.shape[1] != d or weight.numel() != d:
+        raise KernelError("rmsnorm: shapes do not match")
+    if rows is not None:
+        _cuda(rows, "rows", torch.int32)
+        if rows.numel() < n:
+            raise KernelError("rmsnorm: fewer row indices than output rows")
+    elif x.shape[0] < n:
+        raise KernelError("rmsnorm: fewer input rows than output rows")
+    _check(_fn("elementwise", "zlm_rmsnorm")(x.data_ptr(), weight.data_ptr(), code(weight.dtype), out.data_ptr(),
+                                             code(out.dtype), _ptr(rows), n, d, eps, weight_offset, _stream()),
+           "rmsnorm")
+
+
+def gated_act(gu: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[t, j] = act(gu[t, j]) * gu[t, I + j] for gu of shape [T, 2I]."""
+    _cuda(gu, "gu"); _cuda(out, "out", gu.dtype)
+    T, I = out.shape
+    if gu.shape != (T, 2 * I):
+        raise KernelError("gated_act: gu must be [T, 2*I]")
+    kind = {"silu": 0, "gelu_tanh": 1}.get(activation)
+    if kind is None:
+        raise KernelError(f"gated_act: activation {activation!r} is not known (silu, gelu_tanh)")
+    _check(_fn("elementwise", "zlm_gated_act")(gu.data_ptr(), out.data_ptr(), code(gu.dtype), T, I, kind, _stream()),
+           "gated_act")
+
+
+def add_(y: torch.Tensor, x: torch.Tensor) -> None:
+    _cuda(y, "y", torch.float32); _cuda(x, "x", torch.float32)
+    if y.numel() != x.numel():
+        raise KernelError("add_: sizes differ")
+    _check(_fn("elementwise", "zlm_add")(y.data_ptr(), x.data_ptr(), y.numel(), _stream()), "add_")
+
+
+def convert(src: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(src, "src"); _cuda(out, "out")
+    if src.numel() != out.numel():
+        raise KernelError("convert: sizes differ")
+    _check(_fn("elementwise", "zlm_convert")(src.data_ptr(), code(src.dtype), out.data_ptr(), code(out.dtype),
+                                             src.numel(), _stream()), "convert")
+
+
+# ------------------------------------------------------------------------ gemm
+def gemm_generic(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 accumulate: bool = False) -> None:
+    """out[M,N] (+)= x[M,K] @ w[N,K]^T (+ bias) on the CUDA cores; rows may be strided."""
+    for t, n in ((x, "x"), (w, "w"), (out, "out")):
+        if not t.is_cuda:
+            raise KernelError(f"{n} must be on a CUDA device (there is no CPU path)")
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"{n} must be a matrix with unit column stride")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm: shapes do not match: x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if accumulate and out.dtype != torch.float32:
+        raise KernelError("gemm: accumulation needs a float32 output")
+    if bias is not None:
+        _cuda(bias, "bias")
+        if bias.numel() != N:
+            raise KernelError("gemm: bias length does not match")
+    _check(_fn("gemm_generic", "zlm_gemm_generic")(
+        x.data_ptr(), code(x.dtype), w.data_ptr(), code(w.dtype), _ptr(bias),
+        code(bias.dtype) if bias is not None else F32, out.data_ptr(), code(out.dtype), int(accumulate),
+        M, N, K, x.stride(0) if M > 1 else K, w.stride(0) if N > 1 else K, out.stride(0) if M > 1 else N,
+        _stream()), "gemm_generic")
+
+
+# ------------------------------------------------------------------- attention
+def rope_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary_dim: int,
+               inv_freq: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor,
+               block_table: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+               page_size: int) -> None:
+    """Rotate q and k of qkv[T, (n_heads+2 n_kv) head_dim] in place and store k, v in the cache pages.
+
+    k_pages / v_pages: [n_pages, n_kv, page_size, head_dim] of one layer, or None to store nothing.
+    block_table: int32 [B, stride]; row seq_of_token[t] lists the pages of token t's sequence.
+    """
+    _cuda(qkv, "qkv"); _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError("rope_store: qkv width does not match the head counts")
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() * 2 != rotary_dim:
+            raise KernelError("rope_store: the frequency table must hold rotary_dim/2 entries")
+    page_stride = 0
+    if k_pages is not None:
+        _cuda(k_pages, "k_pages", qkv.dtype); _cuda(v_pages, "v_pages", qkv.dtype)
+        if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+            raise KernelError("rope_store: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+        page_stride = k_pages.stride(0)
+    _check(_fn("attention", "zlm_rope_store")(
+        qkv.data_ptr(), code(qkv.dtype), qkv.stride(0), T, n_heads, n_kv, head_dim, rotary_dim, _ptr(inv_freq),
+        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+        _ptr(k_pages), _ptr(v_pages), page_size, page_stride, _stream()), "rope_store")
+
+
+def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                      window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
+                      block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      page_size: int) -> None:
+    """out[t, h, :] = softmax(q[t,h] . K[start..pos_t] * scale) @ V over the paged cache.
+
+    The queries are the first n_heads*head_dim columns of each row of ``qkv`` (any row stride).
+    """
+    _cuda(out, "out", qkv.dtype); _cuda(k_pages, "k_pages", qkv.dtype); _cuda(v_pages, "v_pages", qkv.dtype)
+    _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    if not qkv.is_cuda or qkv.stride(1) != 1:
+        raise KernelError("attention: q must be on the device with unit column stride")
+    T = out.shape[0]
+    if out.shape[1] != n_heads * head_dim or qkv.shape[1] < n_heads * head_dim:
+        raise KernelError("attention: widths do not match the head counts")
+    if head_dim % 8 or head_dim > 256:
+        raise KernelError(f"attention: head size {head_dim} is not supported (a multiple of 8, at most 256)")
+    if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError("attention: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+    _check(_fn("attention", "zlm_attention_general")(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), code(qkv.dtype), T, n_heads, n_kv, head_dim, scale,
+        int(window or 0), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), page_size, k_pages.stride(0), _stream()),
+        "attention_general")
+
+
+def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
+              window: Optional[int], io) -> None:
+    """Attention of a step's tokens over the cache of the running layer; picks the kernel."""
+    attention_general(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
+                      io.block_table, io.k_pages, io.v_pages, io.page_size)
+
+
+def fast_attention_libraries(dtype: torch.dtype, head_dim: int):
+    return ()
+
+
+def fast_gemm_libraries():
+    return ()
+
+
+def fast_gemm(linear, x: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
+    """Run the product on the tensor-core kernels if they take it; False if they do not."""
+    return False
+
+
+# -------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = the id of the largest logit of row r (lowest id on ties)."""
+    _cuda(out, "out", torch.int32)
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("argmax: logits must be a float32 matrix on the device with unit column stride")
+    rows, V = logits.shape
+    if out.numel() < rows:
+        raise KernelError("argmax: the output is too short")
+    _check(_fn("sampling", "zlm_argmax")(logits.data_ptr(), rows, V, logits.stride(0) if rows > 1 else V,
+                                         out.data_ptr(), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, rng: torch.Tensor, temperature: float, top_k: int = 0,
+           top_p: float = 1.0, min_p: float = 0.0, repetition_penalty: float = 1.0, presence_penalty: float = 0.0,
+           history: Optional[torch.Tensor] = None) -> None:
+    """Draw one id per row.  rng: int64 [rows, 2] of (seed, counter).  history: int32 [rows, window], -1 = empty.
+
+    The logits are changed in place when a penalty is on.
+    """
+    _cuda(out, "out", torch.int32); _cuda(rng, "rng", torch.int64)
+    if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be a float32 matrix on the device with unit column stride")
+    rows, V = logits.shape
+    if out.numel() < rows or rng.numel() < 2 * rows:
+        raise KernelError("sample: output or rng too short")
+    if not temperature > 0:
+        raise KernelError("sample: the temperature must be positive (use argmax for greedy)")
+    if top_k > 1024:
+        raise KernelError("sample: top_k above 1024 is not supported")
+    if top_k == 0 and top_p < 1.0:
+        raise KernelError("sample: top_p below 1 needs a top_k between 1 and 1024")
+    window = 0
+    if history is not None:
+        _cuda(history, "history", torch.int32)
+        window = history.shape[1]
+        if history.shape[0] < rows or window > 1024:
+            raise KernelError("sample: history must be [rows, window] with window <= 1024")
+    _check(_fn("sampling", "zlm_sample")(
+        logits.data_ptr(), rows, V, logits.stride(0) if rows > 1 else V, temperature, int(top_k), top_p, min_p,
+        repetition_penalty, presence_penalty, _ptr(history), window, rng.data_ptr(), out.data_ptr(), _stream()),
+        "sample")

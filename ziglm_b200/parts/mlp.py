@@ -1,0 +1,61 @@
+"""Dense gated feed-forward: down( act(gate(x)) * up(x) ), SwiGLU when act is silu.
+
+The reference computes g = W_g x, u = W_u x, act_j = silu(g_j) u_j with
+silu(z) = z/(1+exp(-z)), f = W_d act, no biases (src/model.zig:725-745,
+src/math.zig:1108-1117); its GPU path applies the tanh GELU to every
+architecture (src/cuda_model.zig:695,1379), which is not reproduced.  Gate and
+up are one matrix product over the concatenated weight [gate; up]; the
+activation is a parameter of the part.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import kernels
+from ..config.spec import FeedForwardSpec
+from .base import ParamDecl, Part, register_feed_forward
+from .linear import Linear
+
+
+class GatedMLP(Part):
+    def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device: torch.device):
+        super().__init__(spec, dtype, device)
+        if spec.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated_mlp: activation {spec.activation!r} is not known (silu, gelu_tanh)")
+        if spec.bias:
+            raise ValueError("gated_mlp: biases are not supported")
+        self.intermediate = spec.intermediate
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    @classmethod
+    def declare(cls, spec: FeedForwardSpec) -> Dict[str, ParamDecl]:
+        return {"gate.weight": ParamDecl((spec.intermediate, spec.width)),
+                "up.weight": ParamDecl((spec.intermediate, spec.width)),
+                "down.weight": ParamDecl((spec.width, spec.intermediate))}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        g, u = tensors["gate.weight"], tensors["up.weight"]
+        wide = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+        self.gate_up = Linear(torch.cat([g.to(wide), u.to(wide)], dim=0))
+        self.down = Linear(tensors["down.weight"])
+
+    def kernel_libraries(self) -> Tuple[str, ...]:
+        libs = ("elementwise",)
+        for lin in (self.gate_up, self.down):
+            if lin is not None:
+                libs += lin.libraries(self.dtype)
+        return libs
+
+    def forward(self, step, h: torch.Tensor, residual: torch.Tensor) -> None:
+        T = h.shape[0]
+        gu = step.ws.buf("gate_up", (T, 2 * self.intermediate), self.dtype)
+        self.gate_up(h, gu)
+        act = step.ws.buf("ffn_act", (T, self.intermediate), self.dtype)
+        kernels.gated_act(gu, act, self.spec.activation)
+        self.down(act, residual, accumulate=True)
+
+
+register_feed_forward("gated_mlp", GatedMLP)
