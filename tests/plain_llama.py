@@ -98,25 +98,30 @@ def apply_rope(x: torch.Tensor, positions: Sequence[int], inv_freq: torch.Tensor
     return out
 
 
-def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-              window: Optional[int] = None) -> torch.Tensor:
-    """q: [T, nh, hd]; k, v: [T, nkv, hd], all of one sequence in order.  kvh = h // (nh/nkv); scores
+def attention_row(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                  window: Optional[int] = None) -> torch.Tensor:
+    """One token: q [nh, hd] at position p = len(k)-1 over keys k, v [p+1, nkv, hd].  kvh = h // (nh/nkv);
     s_t = (q . k_t) * scale over t in [start, p]; softmax with max subtraction; o = sum p_t v_t
     (src/model.zig:554,659-700; softmax src/math.zig:1088-1106)."""
-    T, nh, hd = q.shape
+    nh, hd = q.shape
     nkv = k.shape[1]
     group = nh // nkv
-    out = torch.zeros(T, nh, hd, dtype=torch.float32)
-    for p in range(T):
-        start = 0 if window is None else max(0, p - window + 1)
-        for h in range(nh):
-            kvh = h // group
-            keys = k[start:p + 1, kvh]                       # [n, hd]
-            s = (keys @ q[p, h]) * scale
-            e = torch.exp(s - s.max())
-            prob = e / e.sum()
-            out[p, h] = prob @ v[start:p + 1, kvh]
+    p = k.shape[0] - 1
+    start = 0 if window is None else max(0, p - window + 1)
+    out = torch.zeros(nh, hd, dtype=torch.float32)
+    for h in range(nh):
+        kvh = h // group
+        s = (k[start:p + 1, kvh] @ q[h]) * scale
+        e = torch.exp(s - s.max())
+        prob = e / e.sum()
+        out[h] = prob @ v[start:p + 1, kvh]
     return out
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+              window: Optional[int] = None) -> torch.Tensor:
+    """q: [T, nh, hd]; k, v: [T, nkv, hd], all of one sequence in order: every token over the keys up to itself."""
+    return torch.stack([attention_row(q[p], k[:p + 1], v[:p + 1], scale, window) for p in range(q.shape[0])])
 
 
 def silu(z: torch.Tensor) -> torch.Tensor:

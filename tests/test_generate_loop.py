@@ -1,0 +1,128 @@
+"""The generation loop's decisions, on a backend that needs no GPU."""
+from typing import List
+
+import pytest
+
+from ziglm_b200.engine.generate import GenerationOptions, plan_batch, run_generation
+from ziglm_b200.sampling import SamplerParams
+
+
+class FakeBackend:
+    """Next token = (sum of the sequence so far) mod vocab; records every step and slot."""
+
+    def __init__(self, n_slots: int, vocab: int = 50):
+        self.free = list(range(n_slots))
+        self.held = {}
+        self.vocab = vocab
+        self.steps: List[list] = []
+        self.freed: List[int] = []
+
+    def alloc_slot(self):
+        assert self.free, "the loop asked for more slots than exist"
+        s = self.free.pop(0)
+        self.held[s] = []
+        return s
+
+    def free_slot(self, s):
+        assert s in self.held, "slot freed twice or never held"
+        del self.held[s]
+        self.free.append(s)
+        self.free.sort()
+        self.freed.append(s)
+
+    def step_and_sample(self, entries, requests, histories, counters, params):
+        self.steps.append([(s, list(t)) for s, t in entries])
+        out = []
+        for (s, toks), h in zip(entries, histories):
+            assert s in self.held
+            self.held[s].extend(toks)
+            assert self.held[s] == list(h), "the history handed to the sampler is the sequence so far"
+            out.append(sum(self.held[s]) % self.vocab)
+        return out
+
+
+def expected(prompt, n, vocab=50, stop=()):
+    seq, out = list(prompt), []
+    while len(out) < n:
+        t = sum(seq) % vocab
+        if t in stop:
+            return out, "stop"
+        out.append(t); seq.append(t)
+    return out, "length"
+
+
+def run(prompts, opts, n_slots=4, max_tokens=4096, max_seq_len=512, stop_ids=(), callback=None):
+    b = FakeBackend(n_slots)
+    res, stats = run_generation(b, prompts, opts, stop_ids, n_slots, max_tokens, max_seq_len, 64, callback)
+    assert not b.held and sorted(b.free) == list(range(n_slots)), "every slot came back"
+    return b, res, stats
+
+
+def test_unequal_prompts_start_together_then_one_token_each():
+    prompts = [[1, 2, 3], [4], [5, 6, 7, 8, 9]]
+    b, res, stats = run(prompts, GenerationOptions(max_tokens=4, sampler=SamplerParams(greedy=True)))
+    assert b.steps[0] == [(0, [1, 2, 3]), (1, [4]), (2, [5, 6, 7, 8, 9])]
+    assert all(len(t) == 1 for step in b.steps[1:] for _, t in step)
+    for p, r in zip(prompts, res):
+        assert (r.tokens, r.finish_reason) == expected(p, 4)
+    assert stats.prompt_tokens == 9 and stats.completion_tokens == 12
+    assert len(b.steps) == 4                                   # prompt step + 3 decode steps
+
+
+def test_stop_token_ends_a_sequence_early_and_is_not_emitted():
+    prompts = [[1, 2, 3], [10, 1], [2, 2]]
+    want = [expected(p, 8, stop={22}) for p in prompts]
+    assert any(r == "stop" for _, r in want) and any(r == "length" for _, r in want)
+    b, res, _ = run(prompts, GenerationOptions(max_tokens=8, stop_tokens=[22]))
+    for w, r in zip(want, res):
+        assert (r.tokens, r.finish_reason) == w and 22 not in r.tokens
+    sizes = [len(s) for s in b.steps]
+    assert sizes == sorted(sizes, reverse=True) and sizes[0] == 3 and sizes[-1] < 3    # the batch shrinks
+
+
+def test_eos_from_the_model_and_ignore_eos():
+    p = [[1, 2, 3]]
+    first = expected(p[0], 1)[0][0]
+    _, res, _ = run(p, GenerationOptions(max_tokens=5), stop_ids=[first])
+    assert res[0].tokens == [] and res[0].finish_reason == "stop"
+    _, res, _ = run(p, GenerationOptions(max_tokens=5, ignore_eos=True), stop_ids=[first])
+    assert len(res[0].tokens) == 5
+
+
+def test_more_requests_than_slots_run_batch_after_batch_and_slots_are_used_again():
+    prompts = [[i + 1, i + 2] for i in range(7)]
+    b, res, _ = run(prompts, GenerationOptions(max_tokens=3), n_slots=3)
+    assert [len(s) for s in b.steps if len(s[0][1]) == 2] == [3, 3, 1]      # three prompt steps
+    assert len(b.freed) == 7 and set(b.freed) == {0, 1, 2}
+    for p, r in zip(prompts, res):
+        assert r.tokens == expected(p, 3)[0]
+
+
+def test_cache_budget_limits_a_batch():
+    lens = [100, 100, 100, 100]
+    assert plan_batch([0, 1, 2, 3], lens, 28, 8, 256, 512, 64) == [0, 1]        # 128 + 128 positions
+    assert plan_batch([2, 3], lens, 28, 8, 256, 512, 64) == [2, 3]
+    assert plan_batch([0, 1, 2, 3], lens, 28, 1, 4096, 512, 64) == [0]
+    with pytest.raises(ValueError):
+        plan_batch([0], [300], 100, 8, 256, 512, 64)
+
+
+def test_context_limit_and_errors():
+    _, res, _ = run([[1] * 10], GenerationOptions(max_tokens=50), max_seq_len=16)
+    assert res[0].finish_reason == "context" and len(res[0].tokens) == 7       # positions 10..16
+    with pytest.raises(ValueError, match="empty"):
+        run([[]], GenerationOptions())
+    with pytest.raises(ValueError, match="holds"):
+        run([[1] * 20], GenerationOptions(), max_seq_len=16)
+
+
+def test_callback_may_end_a_request_and_echo_prompt():
+    seen = []
+
+    def cb(request, token):
+        seen.append((request, token))
+        return not (request == 0 and len([1 for r, _ in seen if r == 0]) == 2)
+
+    _, res, _ = run([[1, 2], [3, 4]], GenerationOptions(max_tokens=5, echo_prompt=True), callback=cb)
+    assert len(res[0].tokens) == 2 + 2 and res[0].tokens[:2] == [1, 2]
+    assert len(res[1].tokens) == 2 + 5

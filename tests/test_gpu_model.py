@@ -1,0 +1,234 @@
+"""The engine against the plain implementation, in float32 and in bfloat16, under every way of cutting
+requests into steps and batches: whole; the last 32 tokens one by one; batches of unequal lengths whose
+shorter requests end earlier, batch after batch so that slots and pages are used again; long decoding;
+the first tokens of a sequence."""
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# request lengths per configuration: a one-token request, lengths around the page size of 64, a long one
+LENGTHS = {"A": [5, 11, 17, 70, 45, 128], "B": [1, 9, 23, 40, 97, 64], "C": [3, 65, 33, 128, 12, 50]}
+
+
+class Zoo:
+    """Model folders, engines and the plain model's logits, made once per (configuration, precision)."""
+
+    def __init__(self, tmp):
+        self.tmp = tmp
+        self.cache = {}
+
+    def get(self, name, dn, **opts):
+        key = (name, dn, tuple(sorted(opts.items())))
+        if key not in self.cache:
+            from ziglm_b200 import Engine, EngineOptions
+            dtype = DTYPES[dn]
+            folder = helpers.make_folder(self.tmp, helpers.CONFIGS[name], 17, dtype, helpers.NORM_JITTER[name])
+            o = dict(dtype=dn, max_tokens=1024, max_batch=8)
+            o.update(opts)
+            self.cache[key] = (folder, Engine.load(folder, EngineOptions(**o)))
+        return self.cache[key]
+
+    def requests(self, name):
+        V = helpers.CONFIGS[name]["vocab_size"]
+        return [helpers.random_tokens(n, V, 100 + i) for i, n in enumerate(LENGTHS[name])]
+
+    def plain(self, name, dn):
+        key = ("plain", name, dn)
+        if key not in self.cache:
+            folder, _ = self.get(name, dn)
+            act = None if dn == "float32" else torch.bfloat16
+            self.cache[key] = [helpers.plain_logits(folder, r, act=act) for r in self.requests(name)]
+        return self.cache[key]
+
+
+@pytest.fixture(scope="module")
+def zoo(tmp_path_factory):
+    return Zoo(tmp_path_factory.mktemp("models"))
+
+
+CASES = [(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")]
+
+
+@pytest.mark.parametrize("name,dn", CASES)
+def test_each_request_alone_and_whole(zoo, name, dn):
+    _, eng = zoo.get(name, dn)
+    for req, want in zip(zoo.requests(name), zoo.plain(name, dn)):
+        slot = eng.alloc_slot()
+        got = eng.step([(slot, req)], [list(range(len(req)))]).clone()
+        eng.free_slot(slot)
+        helpers.assert_close(got, want, DTYPES[dn], f"{name} {dn} whole, {len(req)} tokens")
+    eng.cache.slots.check()
+
+
+@pytest.mark.parametrize("name,dn", CASES)
+def test_last_32_tokens_one_by_one(zoo, name, dn):
+    _, eng = zoo.get(name, dn)
+    for req, want in zip(zoo.requests(name), zoo.plain(name, dn)):
+        head = max(1, len(req) - 32)
+        slot = eng.alloc_slot()
+        rows = [eng.step([(slot, req[:head])], [list(range(head))]).clone()]
+        for t in req[head:]:
+            rows.append(eng.step([(slot, [t])]).clone())
+        eng.free_slot(slot)
+        got = torch.cat(rows)
+        helpers.assert_close(got, want, DTYPES[dn], f"{name} {dn} tail one by one, {len(req)} tokens")
+        # the first wrong place, if any, is named by assert_close; the prompt's end is row head-1, the first
+        # decoded token row head
+
+
+def run_batches(eng, requests, batches, prompt_lens):
+    """Replay ``requests`` in ``batches`` (lists of request indices): the first step of a batch brings each
+    request's first ``prompt_lens[r]`` tokens, then every live request brings one token a step; a request ends
+    when its tokens are used up and gives its slot back at once.  Returns logits per request, all places."""
+    out = {}
+    for batch in batches:
+        slots = {r: eng.alloc_slot() for r in batch}
+        used = {r: 0 for r in batch}
+        rows = {r: [] for r in batch}
+        live = list(batch)
+        first = True
+        while live:
+            entries, want = [], []
+            for r in live:
+                n = prompt_lens[r] if first else 1
+                entries.append((slots[r], requests[r][used[r]:used[r] + n]))
+                want.append(list(range(n)))
+            logits = eng.step(entries, want).clone()
+            at = 0
+            for r, (_, toks) in zip(live, entries):
+                rows[r].append(logits[at:at + len(toks)])
+                at += len(toks)
+                used[r] += len(toks)
+            first = False
+            for r in list(live):
+                if used[r] == len(requests[r]):
+                    eng.free_slot(slots[r])
+                    live.remove(r)
+        for r in batch:
+            out[r] = torch.cat(rows[r])
+    return out
+
+
+@pytest.mark.parametrize("name,dn", CASES)
+def test_batches_of_unequal_lengths_with_slots_used_again(zoo, name, dn):
+    # three slots and few pages: the second and third batch run in slots and pages the first one left
+    _, eng = zoo.get(name, dn, max_batch=3, max_tokens=448)
+    reqs = zoo.requests(name)
+    prompt_lens = [max(1, len(r) - k) for r, k in zip(reqs, (3, 9, 0, 20, 33, 40))]
+    prompt_lens = [min(p, len(r)) for p, r in zip(prompt_lens, reqs)]
+    order = sorted(range(len(reqs)), key=lambda r: len(reqs[r]))
+    batches = [[order[0], order[5], order[2]], [order[4], order[1]], [order[3]]]
+    got = run_batches(eng, reqs, batches, prompt_lens)
+    for r, want in enumerate(zoo.plain(name, dn)):
+        helpers.assert_close(got[r], want, DTYPES[dn], f"{name} {dn} batched, request {r} of {len(reqs[r])} tokens")
+    eng.cache.slots.check()
+    assert eng.cache.slots.slots.n_held == 0 and all(g.pages.pool.n_held == 0 for g in eng.cache.groups)
+
+
+@pytest.mark.parametrize("name,dn", [("A", "float32"), ("B", "float32"), ("C", "float32")])
+def test_float32_does_not_depend_on_the_schedule(zoo, name, dn):
+    """In 32-bit the three schedules agree to the last few bits: every output element is summed in one fixed order."""
+    _, eng = zoo.get(name, dn)
+    reqs = zoo.requests(name)
+    whole = []
+    for req in reqs:
+        slot = eng.alloc_slot()
+        whole.append(eng.step([(slot, req)], [list(range(len(req)))]).clone())
+        eng.free_slot(slot)
+    got = run_batches(eng, reqs, [[0, 1, 2, 3], [4, 5]], [max(1, len(r) // 2) for r in reqs])
+    for r in range(len(reqs)):
+        assert (got[r] - whole[r]).abs().max().item() <= 1e-6
+
+
+@pytest.mark.parametrize("name,dn", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16"), ("B", "float32")])
+def test_long_decoding(zoo, name, dn):
+    _, eng = zoo.get(name, dn)
+    V = helpers.CONFIGS[name]["vocab_size"]
+    n = min(200, helpers.CONFIGS[name]["max_position_embeddings"])
+    toks = helpers.random_tokens(n, V, 999)
+    folder, _ = zoo.get(name, dn)
+    want = helpers.plain_logits(folder, toks, act=None if dn == "float32" else torch.bfloat16)
+    slot = eng.alloc_slot()
+    rows = [eng.step([(slot, toks[:3])], [[0, 1, 2]]).clone()]
+    for t in toks[3:]:
+        rows.append(eng.step([(slot, [t])]).clone())
+    eng.free_slot(slot)
+    helpers.assert_close(torch.cat(rows), want, DTYPES[dn], f"{name} {dn} long decoding")
+
+
+@pytest.mark.parametrize("name,dn", CASES)
+def test_first_tokens_of_a_sequence(zoo, name, dn):
+    folder, eng = zoo.get(name, dn)
+    V = helpers.CONFIGS[name]["vocab_size"]
+    act = None if dn == "float32" else torch.bfloat16
+    for toks in ([V - 1], [0, 0], [5, V - 1, 5]):
+        want = helpers.plain_logits(folder, toks, act=act)
+        slot = eng.alloc_slot()
+        rows = [eng.step([(slot, [t])]).clone() for t in toks]       # from the very first token, one by one
+        eng.free_slot(slot)
+        helpers.assert_close(torch.cat(rows), want, DTYPES[dn], f"{name} {dn} first tokens {toks}")
+        slot = eng.alloc_slot()
+        got = eng.step([(slot, toks)], [list(range(len(toks)))]).clone()
+        eng.free_slot(slot)
+        helpers.assert_close(got, want, DTYPES[dn], f"{name} {dn} first tokens whole {toks}")
+
+
+def test_wanted_places_and_nothing_wanted(zoo):
+    folder, eng = zoo.get("A", "float32")
+    toks = helpers.random_tokens(20, 256, 3)
+    want = helpers.plain_logits(folder, toks)
+    a, b = eng.alloc_slot(), eng.alloc_slot()
+    got = eng.step([(a, toks[:12]), (b, toks[:7])], [[11, 0, 5], []]).clone()
+    helpers.assert_close(got, want[[11, 0, 5]], torch.float32, "wanted places in the order asked")
+    assert eng.step([(a, toks[12:15]), (b, toks[7:9])], [[], []]) is None
+    got = eng.step([(b, toks[9:10]), (a, toks[15:16])]).clone()
+    helpers.assert_close(got, want[[9, 15]], torch.float32, "default: the last token of each")
+    eng.free_slot(a); eng.free_slot(b)
+
+
+def test_step_refuses_bad_input(zoo):
+    from ziglm_b200 import StepError
+    from ziglm_b200.cache import CacheError, CacheFull, SequenceTooLong
+    _, eng = zoo.get("A", "float32", max_batch=2, max_tokens=128)
+    s = eng.alloc_slot()
+    with pytest.raises(StepError, match="vocabulary"):
+        eng.step([(s, [256])])
+    with pytest.raises(StepError, match="at least one token"):
+        eng.step([(s, [])])
+    with pytest.raises(StepError, match="twice"):
+        eng.step([(s, [1]), (s, [2])])
+    with pytest.raises(StepError, match="outside"):
+        eng.step([(s, [1, 2])], [[2]])
+    with pytest.raises(CacheError):
+        eng.step([(1, [1])])                                   # a slot nobody holds
+    with pytest.raises(SequenceTooLong):
+        eng.step([(s, [1] * 129)])
+    t = eng.alloc_slot()
+    eng.step([(s, [1] * 65)])
+    with pytest.raises(CacheFull):
+        eng.step([(t, [1] * 65)])                              # 2 pages each, the cache has 2
+    assert eng.length(s) == 65 and eng.length(t) == 0
+    eng.free_slot(s); eng.free_slot(t)
+    eng.cache.slots.check()
+
+
+def test_single_sequence_calls_of_the_reference(zoo):
+    folder, eng = zoo.get("B", "float32")
+    toks = helpers.random_tokens(10, 384, 8)
+    want = helpers.plain_logits(folder, toks)
+    eng.reset()
+    l = eng.prefill(toks[:6]).clone()
+    helpers.assert_close(l, want[5], torch.float32, "prefill")
+    for pos in range(6, 10):
+        l = eng.decode(toks[pos], pos).clone()
+        helpers.assert_close(l, want[pos], torch.float32, f"decode at {pos}")
+    from ziglm_b200 import StepError
+    with pytest.raises(StepError, match="position"):
+        eng.decode(1, 3)
+    eng.reset()
+    helpers.assert_close(eng.prefill(toks[:2]).clone(), want[1], torch.float32, "after reset")
+    eng.reset()

@@ -91,7 +91,9 @@ class Engine:
         self._host_events = [None, None]
         self._dev: Optional[torch.Tensor] = None
         self._flip = 0
-        self._graphs: Dict[Tuple[int, int], object] = {}
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graph_kernels = 0
+        self.last_step_h2d_bytes = 0
         self._default_slot: Optional[int] = None
         kernels.require(model.kernel_libraries())
 
@@ -192,6 +194,10 @@ class Engine:
         B = len(slots)
         single = all(len(t) == 1 for t in new_tokens)
         max_total = max(p + len(t) for p, t in zip(past, new_tokens))
+        if single and want_rows == list(range(B)) and self.options.use_graphs:
+            logits = self._graph_step(slots, past, new_tokens, want_rows)
+            self.cache.slots.advance(growth)
+            return logits
         width = -(-max_total // self.cache.page_size)
         widths = tuple(width for _ in self.cache.groups)
         layout = BatchLayout(T, B, len(want_rows), widths)
@@ -201,18 +207,51 @@ class Engine:
         pack_batch(layout, host, slots, past, new_tokens, want_rows, tables)
         dev[:layout.total].copy_(host[:layout.total], non_blocking=True)
         self._host_events[self._flip].record()
-        v = views(layout, dev)
-        step = StepContext(
-            n_tokens=T, n_seqs=B, n_want=len(want_rows), tokens=v["tokens"], positions=v["positions"],
-            seq_of_token=v["seq_of_token"], cu_seqlens=v["cu_seqlens"], past_lens=v["past_lens"],
-            total_lens=v["total_lens"], slots=v["slots"], want_rows=v["want_rows"], block_tables=v["block_tables"],
-            single_token=single, max_new=max(len(t) for t in new_tokens), max_total=max_total, dtype=self.dtype,
-            device=self.device, ws=self.ws, host_past_lens=past, host_new_lens=[len(t) for t in new_tokens],
-            host_slots=slots)
-        step.io = [self.cache.io_for(place, step.block_tables) for place in range(len(self.spec.schedule))]
+        self.last_step_h2d_bytes = layout.total * 4
+        step = self._context(layout, dev, single, max(len(t) for t in new_tokens), max_total, self.ws, past,
+                             [len(t) for t in new_tokens], slots)
         logits = self.model.forward(step)
         self.cache.slots.advance(growth)
         return logits
+
+    def _context(self, layout: BatchLayout, dev: torch.Tensor, single: bool, max_new: int, max_total: int,
+                 ws: Workspace, past: List[int], new_lens: List[int], slots: List[int]) -> StepContext:
+        v = views(layout, dev)
+        step = StepContext(
+            n_tokens=layout.n_tokens, n_seqs=layout.n_seqs, n_want=layout.n_want, tokens=v["tokens"],
+            positions=v["positions"], seq_of_token=v["seq_of_token"], cu_seqlens=v["cu_seqlens"],
+            past_lens=v["past_lens"], total_lens=v["total_lens"], slots=v["slots"], want_rows=v["want_rows"],
+            block_tables=v["block_tables"], single_token=single, max_new=max_new, max_total=max_total,
+            dtype=self.dtype, device=self.device, ws=ws, host_past_lens=past, host_new_lens=new_lens,
+            host_slots=slots)
+        step.io = [self.cache.io_for(place, step.block_tables) for place in range(len(self.spec.schedule))]
+        return step
+
+    # ------------------------------------------------------- decode steps as CUDA graphs
+    def _graph_step(self, slots: List[int], past: List[int], new_tokens: List[List[int]],
+                    want_rows: List[int]) -> torch.Tensor:
+        """A step in which every sequence brings one token and every logit row is wanted: the launches of
+        such a step depend on the batch size alone (everything else is read from device memory), so they are
+        captured once per batch size and replayed (the reference does this for its one sequence,
+        src/cuda_model.zig:1017-1069)."""
+        B = len(slots)
+        g = self._graphs.get(B)
+        if g is None:
+            g = _DecodeGraph(self, B)
+            self._graphs[B] = g
+        width = self.cache.max_pages_per_seq
+        tables = [self.cache.block_table_rows(gi, slots, width) for gi in range(len(self.cache.groups))]
+        host = g.staging()
+        pack_batch(g.layout, host, slots, past, new_tokens, want_rows, tables)
+        g.dev.copy_(host, non_blocking=True)
+        g.mark_copied()
+        self.last_step_h2d_bytes = g.layout.total * 4
+        return g.run(past, slots)
+
+    def graph_launched_kernels(self) -> int:
+        """Kernels launched by graph replays since the counter was last read."""
+        n, self._graph_kernels = self._graph_kernels, 0
+        return n
 
     def _buffers(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """A pinned staging buffer that no copy in flight still reads, and the device buffer."""
@@ -256,3 +295,56 @@ class Engine:
     def generate(self, prompts, options=None, callback=None):
         from .generate import generate
         return generate(self, prompts, options, callback)
+
+
+class _DecodeGraph:
+    """The captured launches of a decode step of one batch size, with the memory they point to."""
+
+    def __init__(self, engine: Engine, batch: int):
+        self.engine = engine
+        self.batch = batch
+        width = engine.cache.max_pages_per_seq
+        self.layout = BatchLayout(batch, batch, batch, tuple(width for _ in engine.cache.groups))
+        self.dev = torch.empty(self.layout.total, dtype=torch.int32, device=engine.device)
+        self.host = [torch.empty(self.layout.total, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.events = [torch.cuda.Event(), torch.cuda.Event()]
+        self.used = [False, False]
+        self.flip = 0
+        self.ws = Workspace(engine.device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.kernels_per_replay = 0
+
+    def staging(self) -> torch.Tensor:
+        self.flip ^= 1
+        if self.used[self.flip]:
+            self.events[self.flip].synchronize()
+        return self.host[self.flip]
+
+    def mark_copied(self) -> None:
+        self.events[self.flip].record()
+        self.used[self.flip] = True
+
+    def _context(self, past: List[int], slots: List[int]) -> StepContext:
+        e = self.engine
+        return e._context(self.layout, self.dev, True, 1, e.max_seq_len, self.ws, past, [1] * self.batch, slots)
+
+    def run(self, past: List[int], slots: List[int]) -> torch.Tensor:
+        e = self.engine
+        if self.graph is not None:
+            self.graph.replay()
+            e._graph_kernels += self.kernels_per_replay
+            return self.logits
+        # first step of this batch size: run it as it is (this also sizes the scratch), then capture it
+        step = self._context(past, slots)
+        before = kernels.launches()
+        logits = e.model.forward(step)
+        self.kernels_per_replay = kernels.launches() - before
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = e.model.forward(self._context(past, slots))
+        kernels.reset_launches_by(self.kernels_per_replay)
+        assert captured.data_ptr() == logits.data_ptr()
+        self.graph, self.logits = graph, logits
+        return logits

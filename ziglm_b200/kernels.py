@@ -34,6 +34,12 @@ def reset_launches() -> None:
     _launches = 0
 
 
+def reset_launches_by(n: int) -> None:
+    """Take back ``n`` counted launches (calls recorded into a CUDA graph launch nothing)."""
+    global _launches
+    _launches -= n
+
+
 def code(dtype: torch.dtype) -> int:
     try:
         return _DTYPE_CODE[dtype]
