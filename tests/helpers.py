@@ -40,7 +40,8 @@ CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
 
 def make_folder(tmp_path, cfg: dict, seed: int, dtype: torch.dtype, norm_jitter: float = 0.0, std: float = 0.02) -> str:
     from ziglm_b200 import config_from_dict, write_random_model
-    folder = os.path.join(str(tmp_path), f"model_{seed}_{str(dtype).split('.')[-1]}")
+    tag = f"{cfg['hidden_size']}x{cfg['num_hidden_layers']}x{cfg['vocab_size']}"
+    folder = os.path.join(str(tmp_path), f"model_{tag}_{seed}_{str(dtype).split('.')[-1]}_{norm_jitter}_{std}")
     write_random_model(folder, config_from_dict(cfg), seed, dtype=dtype, std=std, norm_jitter=norm_jitter)
     return folder
 

@@ -1,0 +1,606 @@
+// Attention over the paged bf16 cache on the tensor cores, head sizes 64 and 128.
+//
+// Two kernels share one inner step.  A page of the cache (64 positions of one
+// key/value head) is brought into shared memory by TMA with the 128-byte swizzle,
+// through a ring of stages guarded by mbarriers (a producer warp issues the copies,
+// four consumer warps compute).  The scores S = Q K^T and the sum O += P V are
+// mma.sync m16n8k16 (bf16 in, float out) with ldmatrix reading the swizzled tiles;
+// the softmax is the running-maximum form in float, in base 2 with the scale folded
+// in.  The formulas are those of the plain kernel in attention.cu (the reference's
+// src/model.zig:659-700): scores scaled after the dot product, keys [start, pos]
+// visible, softmax with maximum subtraction, weighted sum of values; query head h
+// reads key/value head h / (n_heads / n_kv_heads).
+//
+//   decode   one block per (split, kv head, token).  The rows of the tile are the
+//            query heads that share the kv head (up to 16), so the keys and values
+//            are read once for all of them.  The four warps take 16 keys each of
+//            every page.  The key range of a long sequence is split over blocks;
+//            each writes an unnormalised partial result (o, m, l) to scratch and a
+//            second kernel merges the splits in order.
+//   prefill  one block per (query tile of 64 tokens, head, sequence); each warp owns
+//            16 query rows and walks the pages up to its last row's position.
+//
+// Probabilities are rounded to bf16 before they multiply the values, as the
+// tensor-core instruction needs; everything else stays in float.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace zlm {
+using namespace tc;
+
+constexpr int PAGE = 64;
+constexpr int ATC_CONSUMERS = 4;
+constexpr int ATC_THREADS = (ATC_CONSUMERS + 1) * 32;
+constexpr int ERR_ATT_FULL = 11, ERR_ATT_EMPTY = 12;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A [64 keys x HD] tile is HD/64 boxes of 64 rows x 128 bytes, each stored with the
+// 128-byte swizzle: the 16-byte chunk c of row r lies at chunk (c ^ (r & 7)).
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, int key, int chunk) {
+    return base + ((chunk >> 3) << 13) + (key << 7) + ((((chunk & 7) ^ (key & 7))) << 4);
+}
+
+template <int HD, int NSTAGES> struct AtcCfg {
+    static constexpr int TILE_BYTES = PAGE * HD * 2;             // one page of keys (or values) of one head
+    static constexpr int STAGES = NSTAGES;
+    static constexpr int SMEM = 1024 + STAGES * 2 * TILE_BYTES + 256;
+};
+// decode streams the cache and wants many copies in flight; a prompt block is compute-bound and
+// leaves room for several blocks per SM instead
+template <int HD> using DecodeCfg = AtcCfg<HD, HD == 128 ? 4 : 6>;
+template <int HD> using PrefillCfg = AtcCfg<HD, 2>;
+
+// Query fragments of 16 rows straight from global memory: row pointers may differ per row.
+template <int HD>
+__device__ __forceinline__ void load_q_frags(uint32_t (&qf)[HD / 16][4], const __nv_bfloat16* row_lo,
+                                             const __nv_bfloat16* row_hi, int tid4) {
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        const int c = ks * 16 + 2 * tid4;
+        qf[ks][0] = row_lo ? *reinterpret_cast<const uint32_t*>(row_lo + c) : 0u;
+        qf[ks][1] = row_hi ? *reinterpret_cast<const uint32_t*>(row_hi + c) : 0u;
+        qf[ks][2] = row_lo ? *reinterpret_cast<const uint32_t*>(row_lo + c + 8) : 0u;
+        qf[ks][3] = row_hi ? *reinterpret_cast<const uint32_t*>(row_hi + c + 8) : 0u;
+    }
+}
+
+// One step of the running softmax for a warp's 16 rows over NT*8 keys of the page in shared memory.
+//   key0        first key (row of the tile) this warp reads
+//   gkey0       position in the sequence of that key
+//   lim_lo/hi   last visible position of rows gid / gid+8;  start_lo/hi first visible one
+template <int HD, int NT>
+__device__ __forceinline__ void page_step(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, uint32_t v_tile, int key0,
+                                          int gkey0, int lim_lo, int lim_hi, int start_lo, int start_hi,
+                                          float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HD / 8][4],
+                                          int lane) {
+    const int gid = lane >> 2, tid4 = lane & 3, mi = lane >> 3, r8 = lane & 7;
+    float s[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+            uint32_t kf[4];
+            ldsm_x4(kf, tile_addr(k_tile, key0 + np * 16 + ((mi >> 1) << 3) + r8, 2 * ks + (mi & 1)));
+            mma_16816(s[2 * np], qf[ks], kf[0], kf[1]);
+            mma_16816(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = gkey0 + nt * 8 + 2 * tid4 + (i & 1);
+            const bool hi = i >= 2;
+            const bool vis = key <= (hi ? lim_hi : lim_lo) && key >= (hi ? start_hi : start_lo);
+            s[nt][i] = vis ? s[nt][i] * scale_log2 : -INFINITY;
+            mx[hi] = fmaxf(mx[hi], s[nt][i]);
+        }
+    }
+    float corr[2], use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m[h], mx[h]);
+        use[h] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen no key yet
+        corr[h] = exp2f(m[h] - use[h]);                      // exp2(-inf) = 0 the first time
+        m[h] = m_new;
+        l[h] *= corr[h];
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            s[nt][i] = exp2f(s[nt][i] - use[i >> 1]);
+            l[i >> 1] += s[nt][i];
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kp = 0; kp < NT / 2; ++kp) {
+        uint32_t pf[4];
+        pf[0] = pack_bf16(s[2 * kp][0], s[2 * kp][1]);
+        pf[1] = pack_bf16(s[2 * kp][2], s[2 * kp][3]);
+        pf[2] = pack_bf16(s[2 * kp + 1][0], s[2 * kp + 1][1]);
+        pf[3] = pack_bf16(s[2 * kp + 1][2], s[2 * kp + 1][3]);
+#pragma unroll
+        for (int j = 0; j < HD / 16; ++j) {
+            uint32_t vf[4];
+            ldsm_x4_trans(vf, tile_addr(v_tile, key0 + kp * 16 + ((mi & 1) << 3) + r8, 2 * j + (mi >> 1)));
+            mma_16816(o[2 * j], pf, vf[0], vf[1]);
+            mma_16816(o[2 * j + 1], pf, vf[2], vf[3]);
+        }
+    }
+}
+
+struct AtcCommon {
+    const __nv_bfloat16* q;
+    long q_row_stride;
+    int n_heads, n_kv;
+    float scale_log2;
+    int window;
+    const int* block_table;
+    int bt_stride;
+    int* err;
+};
+
+// The producer warp: copies the pages [page_lo, page_hi) of one kv head into the ring.
+template <int HD, typename C>
+__device__ __forceinline__ void produce_pages(const CUtensorMap* tk, const CUtensorMap* tv, const int* bt, int n_kv,
+                                              int kvh, int page_lo, int page_hi, uint32_t k0, uint32_t v0,
+                                              uint32_t full0, uint32_t empty0, volatile int* abort_flag, int* err) {
+    int issued = 0;
+    for (int p = page_lo; p < page_hi; ++p, ++issued) {
+        const int s = issued % C::STAGES;
+        const uint32_t ph = (issued / C::STAGES) & 1;
+        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, err, ERR_ATT_EMPTY)) break;
+        const int row = (bt[p] * n_kv + kvh) * PAGE;
+        mbar_expect_tx(full0 + 8 * s, 2 * C::TILE_BYTES);
+#pragma unroll
+        for (int b = 0; b < HD / 64; ++b) {
+            tma_load_2d(k0 + s * C::TILE_BYTES + b * 8192, tk, full0 + 8 * s, b * 64, row);
+            tma_load_2d(v0 + s * C::TILE_BYTES + b * 8192, tv, full0 + 8 * s, b * 64, row);
+        }
+    }
+    if (*abort_flag) {
+        const int first = issued > C::STAGES ? issued - C::STAGES : 0;
+        for (int i = first; i < issued; ++i) {
+            bool landed = false;
+            for (uint32_t n = 0; n < WAIT_POLLS && !landed; ++n)
+                landed = mbar_try_wait(full0 + 8 * (i % C::STAGES), (i / C::STAGES) & 1);
+            if (!landed && err) atomicCAS(err, 0, ERR_WAIT_DRAIN);
+        }
+    }
+}
+
+// ------------------------------------------------------------------- decode
+template <int HD>
+__global__ void __launch_bounds__(ATC_THREADS)
+attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, AtcCommon a,
+                   const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                   float* __restrict__ part_o, float* __restrict__ part_ml) {
+    using C = DecodeCfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t k0 = base, v0 = base + C::STAGES * C::TILE_BYTES;
+    const uint32_t bar = v0 + C::STAGES * C::TILE_BYTES;
+    const uint32_t full0 = bar, empty0 = bar + 8 * C::STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (bar - base) + 16 * C::STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_splits = gridDim.x, split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int group = a.n_heads / a.n_kv;
+    const int pos = positions[t];
+    const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    const int* bt = a.block_table + (long)seq_of_token[t] * a.bt_stride;
+    const int first_page = start / PAGE, end_page = pos / PAGE + 1;
+    const int per = (end_page - first_page + n_splits - 1) / n_splits;
+    const int page_lo = first_page + split * per;
+    const int page_hi = min(end_page, page_lo + per);
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmap_k);
+        prefetch_tmap(&tmap_v);
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, ATC_CONSUMERS);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    const int gid = lane >> 2, tid4 = lane & 3;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+
+    if (warp == ATC_CONSUMERS) {
+        if (lane == 0)
+            produce_pages<HD, C>(&tmap_k, &tmap_v, bt, a.n_kv, kvh, page_lo, page_hi, k0, v0, full0, empty0, abort_flag,
+                              a.err);
+        __syncwarp();
+    } else {
+        // rows of the tile: the query heads of this kv head (rows beyond the group are zero)
+        const __nv_bfloat16* qrow = a.q + (long)t * a.q_row_stride + (long)kvh * group * HD;
+        uint32_t qf[HD / 16][4];
+        load_q_frags<HD>(qf, gid < group ? qrow + gid * HD : nullptr, gid + 8 < group ? qrow + (gid + 8) * HD : nullptr,
+                         tid4);
+        int it = 0;
+        for (int p = page_lo; p < page_hi; ++p, ++it) {
+            const int s = it % C::STAGES;
+            if (!mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL)) break;
+            page_step<HD, 2>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16, pos, pos,
+                             start, start, a.scale_log2, m, l, o, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+            l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+        }
+    }
+    __syncthreads();            // every page has been consumed: the stage memory is free for the merge
+
+    // merge the four warps (each saw a quarter of the keys), rows < group only
+    float* mo = reinterpret_cast<float*>(smem);                       // [4][16][HD]
+    float* mm = mo + ATC_CONSUMERS * 16 * HD;                          // [4][16]
+    float* ml = mm + ATC_CONSUMERS * 16;                               // [4][16]
+    if (warp < ATC_CONSUMERS) {
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            float* r0 = mo + ((warp * 16 + gid) * HD) + n * 8 + 2 * tid4;
+            float* r1 = mo + ((warp * 16 + gid + 8) * HD) + n * 8 + 2 * tid4;
+            r0[0] = o[n][0]; r0[1] = o[n][1];
+            r1[0] = o[n][2]; r1[1] = o[n][3];
+        }
+        if (tid4 == 0) {
+            mm[warp * 16 + gid] = m[0]; mm[warp * 16 + gid + 8] = m[1];
+            ml[warp * 16 + gid] = l[0]; ml[warp * 16 + gid + 8] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
+        const int r = idx / HD, d = idx - r * HD;
+        float big = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATC_CONSUMERS; ++w) big = fmaxf(big, mm[w * 16 + r]);
+        float acc = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATC_CONSUMERS; ++w) {
+            const float mw = mm[w * 16 + r];
+            const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - big);
+            acc += mo[(w * 16 + r) * HD + d] * wgt;
+            den += ml[w * 16 + r] * wgt;
+        }
+        const long row = ((long)t * a.n_heads + kvh * group + r) * n_splits + split;
+        part_o[row * HD + d] = acc;
+        if (d == 0) { part_ml[row * 2] = big; part_ml[row * 2 + 1] = den; }
+    }
+}
+
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order.
+template <int HD>
+__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                  __nv_bfloat16* __restrict__ out, int n_splits) {
+    const long row = blockIdx.x;                    // t * n_heads + h
+    float big = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) big = fmaxf(big, part_ml[(row * n_splits + s) * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f, den = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(row * n_splits + s) * 2];
+            const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - big);
+            acc += part_o[(row * n_splits + s) * HD + d] * wgt;
+            den += part_ml[(row * n_splits + s) * 2 + 1] * wgt;
+        }
+        out[row * HD + d] = __float2bfloat16_rn(acc / den);
+    }
+}
+
+// ------------------------------------------------------------------ prefill
+template <int HD>
+__global__ void __launch_bounds__(ATC_THREADS)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, AtcCommon a,
+                    const int* __restrict__ cu_seqlens, const int* __restrict__ past_lens,
+                    __nv_bfloat16* __restrict__ out) {
+    using C = PrefillCfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t k0 = base, v0 = base + C::STAGES * C::TILE_BYTES;
+    const uint32_t bar = v0 + C::STAGES * C::TILE_BYTES;
+    const uint32_t full0 = bar, empty0 = bar + 8 * C::STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (bar - base) + 16 * C::STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int tok_begin = cu_seqlens[b], n_new = cu_seqlens[b + 1] - tok_begin;
+    // the last query tiles see the most keys: give them the lowest block indices
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * 64;
+    if (q0 >= n_new) return;
+    const int past = past_lens[b];
+    const int kvh = h / (a.n_heads / a.n_kv);
+    const int* bt = a.block_table + (long)b * a.bt_stride;
+    const int rows_here = min(64, n_new - q0);
+    const int pos_first = past + q0, pos_last = past + q0 + rows_here - 1;
+    const int start_first = (a.window > 0 && pos_first - a.window + 1 > 0) ? pos_first - a.window + 1 : 0;
+    const int page_lo = start_first / PAGE, page_hi = pos_last / PAGE + 1;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmap_k);
+        prefetch_tmap(&tmap_v);
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, ATC_CONSUMERS);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    if (warp == ATC_CONSUMERS) {
+        if (lane == 0)
+            produce_pages<HD, C>(&tmap_k, &tmap_v, bt, a.n_kv, kvh, page_lo, page_hi, k0, v0, full0, empty0, abort_flag,
+                              a.err);
+        return;
+    }
+    const int gid = lane >> 2, tid4 = lane & 3;
+    const int r_lo = q0 + warp * 16 + gid, r_hi = r_lo + 8;          // rows within the sequence's new tokens
+    const bool has_lo = r_lo < n_new, has_hi = r_hi < n_new;
+    const __nv_bfloat16* qbase = a.q + (long)h * HD;
+    uint32_t qf[HD / 16][4];
+    load_q_frags<HD>(qf, has_lo ? qbase + (long)(tok_begin + r_lo) * a.q_row_stride : nullptr,
+                     has_hi ? qbase + (long)(tok_begin + r_hi) * a.q_row_stride : nullptr, tid4);
+    const int lim_lo = has_lo ? past + r_lo : -1, lim_hi = has_hi ? past + r_hi : -1;
+    const int st_lo = (a.window > 0 && lim_lo - a.window + 1 > 0) ? lim_lo - a.window + 1 : 0;
+    const int st_hi = (a.window > 0 && lim_hi - a.window + 1 > 0) ? lim_hi - a.window + 1 : 0;
+    // the warp's rows span positions [w_first, w_last]: pages wholly outside need no work
+    const int w_first = past + q0 + warp * 16, w_last = min(pos_last, w_first + 15);
+    const int w_start = (a.window > 0 && w_first - a.window + 1 > 0) ? w_first - a.window + 1 : 0;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+
+    int it = 0;
+    for (int p = page_lo; p < page_hi; ++p, ++it) {
+        const int s = it % C::STAGES;
+        if (!mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL)) break;
+        const bool needed = w_first <= pos_last && p * PAGE <= w_last && p * PAGE + PAGE - 1 >= w_start;
+        if (needed)
+            page_step<HD, 8>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, 0, p * PAGE, lim_lo, lim_hi, st_lo, st_hi,
+                             a.scale_log2, m, l, o, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 1);
+        l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 2);
+    }
+    if (*abort_flag) return;
+    const float inv_lo = has_lo ? 1.f / l[0] : 0.f, inv_hi = has_hi ? 1.f / l[1] : 0.f;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        const int d = n * 8 + 2 * tid4;
+        if (has_lo)
+            *reinterpret_cast<uint32_t*>(out + ((long)(tok_begin + r_lo) * a.n_heads + h) * HD + d) =
+                pack_bf16(o[n][0] * inv_lo, o[n][1] * inv_lo);
+        if (has_hi)
+            *reinterpret_cast<uint32_t*>(out + ((long)(tok_begin + r_hi) * a.n_heads + h) * HD + d) =
+                pack_bf16(o[n][2] * inv_hi, o[n][3] * inv_hi);
+    }
+}
+
+// ------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// The pages of one layer as a matrix [n_pages * n_kv * 64, hd], read in boxes of 64 rows x 64 elements.
+static int page_map(CUtensorMap* out, const void* ptr, long rows, int hd) {
+    struct Key { const void* p; long rows; int hd; };
+    static std::unordered_map<const void*, std::pair<Key, CUtensorMap>> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(ptr);
+    if (it != cache.end() && it->second.first.rows == rows && it->second.first.hd == hd) {
+        *out = it->second.second;
+        return 0;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ZLM_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)PAGE};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ZLM_ERR_BAD_ARG;
+    if (cache.size() > 4096) cache.clear();
+    cache[ptr] = {Key{ptr, rows, hd}, m};
+    *out = m;
+    return 0;
+}
+
+static int* att_error_word() {
+    static int* word = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (cudaMalloc(&word, sizeof(int)) == cudaSuccess) cudaMemset(word, 0, sizeof(int));
+        else word = nullptr;
+    });
+    return word;
+}
+
+template <typename Kern>
+static int set_smem(Kern kern, int bytes, bool* done) {
+    if (*done) return 0;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    *done = true;
+    return 0;
+}
+
+static int fill_common(AtcCommon* a, CUtensorMap* mk, CUtensorMap* mv, const void* q, long q_row_stride, int n_heads,
+                       int n_kv, int hd, float scale, int window, const int* block_table, int bt_stride,
+                       const void* k_pages, const void* v_pages, long n_pages, int page_size) {
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size != PAGE) return ZLM_ERR_BAD_ARG;
+    if (hd != 64 && hd != 128) return ZLM_ERR_UNSUPPORTED;
+    if (((uintptr_t)q % 4) || (q_row_stride % 2) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16))
+        return ZLM_ERR_UNSUPPORTED;
+    int rc = page_map(mk, k_pages, n_pages * n_kv * PAGE, hd);
+    if (rc) return rc;
+    rc = page_map(mv, v_pages, n_pages * n_kv * PAGE, hd);
+    if (rc) return rc;
+    a->q = (const __nv_bfloat16*)q;
+    a->q_row_stride = q_row_stride;
+    a->n_heads = n_heads;
+    a->n_kv = n_kv;
+    a->scale_log2 = scale * 1.4426950408889634f;
+    a->window = window;
+    a->block_table = block_table;
+    a->bt_stride = bt_stride;
+    a->err = att_error_word();
+    return 0;
+}
+
+}  // namespace zlm
+
+using namespace zlm;
+
+// Decode-style attention: every token is a tile of its own (its query heads grouped by kv head).
+// part_o: float [T * n_heads * n_splits * hd], part_ml: float [T * n_heads * n_splits * 2] (scratch).
+ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out, int T, int n_heads, int n_kv, int hd,
+                                    float scale, int window, const int* positions, const int* seq_of_token,
+                                    const int* block_table, int bt_stride, const void* k_pages, const void* v_pages,
+                                    long n_pages, int page_size, int n_splits, float* part_o, float* part_ml,
+                                    cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (n_splits < 1 || n_splits > 65535) return ZLM_ERR_BAD_ARG;
+    if (n_kv > 0 && n_heads / n_kv > 16) return ZLM_ERR_UNSUPPORTED;
+    AtcCommon a;
+    CUtensorMap mk, mv;
+    int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
+                         k_pages, v_pages, n_pages, page_size);
+    if (rc) return rc;
+    dim3 grid(n_splits, n_kv, T);
+    using CFG128 = DecodeCfg<128>;
+    using CFG64 = DecodeCfg<64>;
+    if (hd == 128) {
+        static bool done = false;
+        rc = set_smem(attn_decode_kernel<128>, CFG128::SMEM, &done);
+        if (rc) return rc;
+        attn_decode_kernel<128><<<grid, ATC_THREADS, CFG128::SMEM, stream>>>(mk, mv, a, positions, seq_of_token,
+                                                                                 part_o, part_ml);
+        attn_merge_kernel<128><<<T * n_heads, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits);
+    } else {
+        static bool done = false;
+        rc = set_smem(attn_decode_kernel<64>, CFG64::SMEM, &done);
+        if (rc) return rc;
+        attn_decode_kernel<64><<<grid, ATC_THREADS, CFG64::SMEM, stream>>>(mk, mv, a, positions, seq_of_token,
+                                                                               part_o, part_ml);
+        attn_merge_kernel<64><<<T * n_heads, 64, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits);
+    }
+    return launch_status();
+}
+
+// Prompt attention: B sequences with cu_seqlens[B+1] new tokens each after past_lens[b] cached ones.
+ZLM_EXPORT int zlm_attention_prefill(const void* q, long q_row_stride, void* out, int B, int max_new, int n_heads,
+                                     int n_kv, int hd, float scale, int window, const int* cu_seqlens,
+                                     const int* past_lens, const int* block_table, int bt_stride, const void* k_pages,
+                                     const void* v_pages, long n_pages, int page_size, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    AtcCommon a;
+    CUtensorMap mk, mv;
+    int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
+                         k_pages, v_pages, n_pages, page_size);
+    if (rc) return rc;
+    dim3 grid((max_new + 63) / 64, n_heads, B);
+    if (grid.y > 65535 || grid.z > 65535) return ZLM_ERR_UNSUPPORTED;
+    using CFG128 = PrefillCfg<128>;
+    using CFG64 = PrefillCfg<64>;
+    if (hd == 128) {
+        static bool done = false;
+        rc = set_smem(attn_prefill_kernel<128>, CFG128::SMEM, &done);
+        if (rc) return rc;
+        attn_prefill_kernel<128><<<grid, ATC_THREADS, CFG128::SMEM, stream>>>(mk, mv, a, cu_seqlens, past_lens,
+                                                                                  (__nv_bfloat16*)out);
+    } else {
+        static bool done = false;
+        rc = set_smem(attn_prefill_kernel<64>, CFG64::SMEM, &done);
+        if (rc) return rc;
+        attn_prefill_kernel<64><<<grid, ATC_THREADS, CFG64::SMEM, stream>>>(mk, mv, a, cu_seqlens, past_lens,
+                                                                                (__nv_bfloat16*)out);
+    }
+    return launch_status();
+}
+
+ZLM_EXPORT int zlm_attention_tc_status(int* out) {
+    int* w = att_error_word();
+    if (!w) { *out = -1; return 0; }
+    cudaError_t e = cudaMemcpy(out, w, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int)e;
+    if (*out != 0) cudaMemset(w, 0, sizeof(int));
+    return 0;
+}

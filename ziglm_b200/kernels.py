@@ -66,6 +66,19 @@ _PROTOTYPES = {
         "zlm_attention_general": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
     },
+    "attention_tc": {
+        "zlm_attention_decode": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
+                                 c_void_p, c_void_p],
+        "zlm_attention_prefill": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_void_p],
+        "zlm_attention_tc_status": [c_void_p],
+    },
+    "gemm_tc": {
+        "zlm_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_long,
+                        c_long, c_long, c_int, c_void_p],
+        "zlm_gemm_tc_status": [c_void_p],
+    },
     "sampling": {
         "zlm_argmax": [c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
         "zlm_sample": [c_void_p, c_int, c_int, c_long, c_float, c_int, c_float, c_float, c_float, c_float, c_void_p,
@@ -264,24 +277,171 @@ def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: 
         "attention_general")
 
 
+def _tc_attention_ok(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv > 0 and n_heads % n_kv == 0
+            and n_heads // n_kv <= 16 and page_size == 64)
+
+
+def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                     window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
+                     block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int,
+                     n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor) -> bool:
+    """Tensor-core attention for steps of one token per sequence (bf16, head size 64 or 128).
+
+    Each token's query heads are grouped by key/value head so that the cache is read once per group; the keys
+    of a sequence are split over ``n_splits`` blocks whose partial results go through the float32 scratch
+    ``part_o`` [T*n_heads*n_splits*head_dim] and ``part_ml`` [T*n_heads*n_splits*2].  False if refused.
+    """
+    _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
+    _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    _cuda(part_o, "part_o", torch.float32); _cuda(part_ml, "part_ml", torch.float32)
+    T = out.shape[0]
+    if not qkv.is_cuda or qkv.dtype != torch.bfloat16 or qkv.stride(1) != 1:
+        raise KernelError("attention_decode: q must be bfloat16 on the device with unit column stride")
+    if out.shape[1] != n_heads * head_dim or qkv.shape[1] < n_heads * head_dim or qkv.shape[0] < T:
+        raise KernelError("attention_decode: widths do not match the head counts")
+    if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError("attention_decode: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+    if part_o.numel() < T * n_heads * n_splits * head_dim or part_ml.numel() < T * n_heads * n_splits * 2:
+        raise KernelError("attention_decode: the scratch is too small for this many splits")
+    status = _fn("attention_tc", "zlm_attention_decode")(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, int(window or 0),
+        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+        k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_splits, part_o.data_ptr(),
+        part_ml.data_ptr(), _stream())
+    if status == -2:
+        return False
+    _check(status, "attention_decode")
+    global _launches
+    _launches += 1          # the merge of the splits is a second launch
+    return True
+
+
+def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, n_kv: int,
+                      head_dim: int, scale: float, window: Optional[int], cu_seqlens: torch.Tensor,
+                      past_lens: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                      v_pages: torch.Tensor, page_size: int) -> bool:
+    """Tensor-core attention for prompt steps: sequence b brings tokens cu_seqlens[b]..cu_seqlens[b+1] of the
+    packed stream after past_lens[b] cached ones (bf16, head size 64 or 128).  False if refused."""
+    _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
+    _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(past_lens, "past_lens", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    if not qkv.is_cuda or qkv.dtype != torch.bfloat16 or qkv.stride(1) != 1:
+        raise KernelError("attention_prefill: q must be bfloat16 on the device with unit column stride")
+    if out.shape[1] != n_heads * head_dim or qkv.shape[1] < n_heads * head_dim:
+        raise KernelError("attention_prefill: widths do not match the head counts")
+    if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError("attention_prefill: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+    if cu_seqlens.numel() < n_seqs + 1 or past_lens.numel() < n_seqs:
+        raise KernelError("attention_prefill: sequence arrays are too short")
+    status = _fn("attention_tc", "zlm_attention_prefill")(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), n_seqs, max_new, n_heads, n_kv, head_dim, scale,
+        int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, _stream())
+    if status == -2:
+        return False
+    _check(status, "attention_prefill")
+    return True
+
+
+def attention_tc_status() -> int:
+    """0, or the code of a bounded wait that ran out inside a tensor-core attention kernel (11 a page never
+    landed, 12 a stage never drained, 4 copies still in flight).  Synchronises the device."""
+    out = ctypes.c_int(0)
+    rc = _fn("attention_tc", "zlm_attention_tc_status")(ctypes.byref(out))
+    if rc != 0:
+        raise KernelError(f"attention_tc_status: CUDA error {rc}")
+    return out.value
+
+
+def decode_splits(n_tokens: int, n_kv: int, max_total: int, page_size: int = 64) -> int:
+    """How many blocks share the keys of one sequence in a decode step: enough for two blocks per SM."""
+    pages = max(1, -(-max_total // page_size))
+    want = -(-296 // max(1, n_tokens * n_kv))
+    return max(1, min(want, pages, 64))
+
+
 def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
               window: Optional[int], io) -> None:
     """Attention of a step's tokens over the cache of the running layer; picks the kernel."""
+    if _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
+        if step.single_token:
+            n_splits = decode_splits(step.n_tokens, n_kv, step.max_total, io.page_size)
+            part_o = step.ws.buf("attn_part_o", (step.n_tokens * n_heads * n_splits * head_dim,), torch.float32)
+            part_ml = step.ws.buf("attn_part_ml", (step.n_tokens * n_heads * n_splits * 2,), torch.float32)
+            if attention_decode(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions,
+                                step.seq_of_token, io.block_table, io.k_pages, io.v_pages, io.page_size, n_splits,
+                                part_o, part_ml):
+                return
+        elif attention_prefill(qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window,
+                               step.cu_seqlens, step.past_lens, io.block_table, io.k_pages, io.v_pages,
+                               io.page_size):
+            return
     attention_general(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
                       io.block_table, io.k_pages, io.v_pages, io.page_size)
 
 
 def fast_attention_libraries(dtype: torch.dtype, head_dim: int):
-    return ()
+    return ("attention_tc",) if dtype == torch.bfloat16 and head_dim in (64, 128) else ()
 
 
 def fast_gemm_libraries():
-    return ()
+    return ("gemm_tc",)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            accumulate: bool = False, splits: int = 0) -> bool:
+    """out[T,N] (+)= x[T,K] @ w[N,K]^T (+ bias) on the tcgen05 tensor cores, bf16 operands.
+
+    Returns False, having done nothing, if the operands are not what TMA can read (a row stride that is no
+    multiple of 8 elements, a base address off a 16-byte boundary).
+    """
+    for t, n in ((x, "x"), (w, "w"), (out, "out")):
+        if not t.is_cuda:
+            raise KernelError(f"{n} must be on a CUDA device (there is no CPU path)")
+        if t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"{n} must be a matrix with unit column stride")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc: x and w must be bfloat16")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (T, N):
+        raise KernelError(f"gemm: shapes do not match: x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if accumulate and out.dtype != torch.float32:
+        raise KernelError("gemm: accumulation needs a float32 output")
+    if bias is not None:
+        _cuda(bias, "bias")
+        if bias.numel() != N:
+            raise KernelError("gemm: bias length does not match")
+    status = _fn("gemm_tc", "zlm_gemm_tc")(
+        x.data_ptr(), w.data_ptr(), _ptr(bias), code(bias.dtype) if bias is not None else F32, out.data_ptr(),
+        code(out.dtype), int(accumulate), T, N, K, x.stride(0) if T > 1 else K, w.stride(0) if N > 1 else K,
+        out.stride(0) if T > 1 else N, int(splits), _stream())
+    if status == -2:
+        return False
+    _check(status, "gemm_tc")
+    return True
+
+
+def gemm_tc_status() -> int:
+    """0, or the code of a bounded wait that ran out inside a tensor-core kernel since the last call
+    (1 tile never landed, 2 stage never drained, 3 accumulator never completed, 4 copies still in flight).
+    Synchronises the device."""
+    out = ctypes.c_int(0)
+    rc = _fn("gemm_tc", "zlm_gemm_tc_status")(ctypes.byref(out))
+    if rc != 0:
+        raise KernelError(f"gemm_tc_status: CUDA error {rc}")
+    return out.value
 
 
 def fast_gemm(linear, x: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
     """Run the product on the tensor-core kernels if they take it; False if they do not."""
-    return False
+    if x.dtype != torch.bfloat16 or linear.weight.dtype != torch.bfloat16:
+        return False
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    return gemm_tc(x, linear.weight, out, bias=linear.bias, accumulate=accumulate)
 
 
 # -------------------------------------------------------------------- sampling
