@@ -45,15 +45,17 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
 }
 
 // --------------------------------------------------------- gated activation
-// gu is [T, 2*I]: gate in columns [0, I), up in columns [I, 2I).
+// gu is [T, 2*I].  interleaved == 0: gate in columns [0, I), up in columns [I, 2I);
+// interleaved != 0: gate j in column 2j, up j in column 2j+1.
 template <typename T>
-__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, long total, int I, int kind) {
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, long total, int I, int kind,
+                                 int interleaved) {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const long t = idx / I;
     const int j = (int)(idx - t * I);
-    const float g = to_float(gu[t * 2 * I + j]);
-    const float u = to_float(gu[t * 2 * I + I + j]);
+    const float g = to_float(gu[t * 2 * I + (interleaved ? 2 * j : j)]);
+    const float u = to_float(gu[t * 2 * I + (interleaved ? 2 * j + 1 : I + j)]);
     float a;
     if (kind == 0) {
         a = g / (1.0f + expf(-g));                         // silu
@@ -116,17 +118,20 @@ ZLM_EXPORT int zlm_rmsnorm(const float* x, const void* w, int w_dtype, void* out
     return launch_status();
 }
 
-ZLM_EXPORT int zlm_gated_act(const void* gu, void* out, int dtype, int T, int I, int kind, cudaStream_t stream) {
+ZLM_EXPORT int zlm_gated_act(const void* gu, void* out, int dtype, int T, int I, int kind, int interleaved,
+                             cudaStream_t stream) {
     if (T <= 0) return 0;
     if (I <= 0 || (kind != 0 && kind != 1)) return ZLM_ERR_BAD_ARG;
     const long total = (long)T * I;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == ZLM_F32)
-        gated_act_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, I, kind);
+        gated_act_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, I, kind,
+                                                                 interleaved);
     else if (dtype == ZLM_BF16)
         gated_act_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu,
-                                                                         (__nv_bfloat16*)out, total, I, kind);
+                                                                         (__nv_bfloat16*)out, total, I, kind,
+                                                                         interleaved);
     else
         return ZLM_ERR_UNSUPPORTED;
     return launch_status();

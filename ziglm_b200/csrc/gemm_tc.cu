@@ -9,8 +9,11 @@
 //   warp 1   issues tcgen05.mma (M=128, N=BN, K=16, bf16 -> float) from the stages
 //            into an accumulator in tensor memory, and frees a stage with
 //            tcgen05.commit when its instructions have read it;
-//   warps 2-5 read the accumulator with tcgen05.ld and write the output: plain
-//            store (float or bf16), or sum into a float output (the residual stream).
+//   warps 2-5 read the accumulator with tcgen05.ld, add the bias, stage the tile in
+//            shared memory and hand it to one TMA store (float or bf16 output) or one
+//            TMA reduce-add (sum into a float output: the residual stream).  In the
+//            gated mode the weight rows alternate gate and up rows and the epilogue
+//            writes act(gate) * up, so the activation never makes a trip to memory.
 // When there are too few tiles to occupy the GPU (a decode step against a
 // 4096-row weight), the K range is split over the CTAs of a thread-block cluster;
 // their partial accumulators are summed in rank order through distributed shared
@@ -22,6 +25,7 @@
 #include "common.cuh"
 #include "tc_common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -34,7 +38,7 @@ constexpr int TC_UMMA_K = 16;
 constexpr int TC_THREADS = 192;
 constexpr int A_BYTES = TC_BM * TC_BK * 2;
 
-enum OutMode { OUT_F32 = 0, OUT_F32_ACC = 1, OUT_BF16 = 2 };
+enum OutMode { OUT_F32 = 0, OUT_F32_ACC = 1, OUT_BF16 = 2, OUT_BF16_GLU = 3 };
 
 struct TcArgs {
     const void* bias;
@@ -45,51 +49,79 @@ struct TcArgs {
     int kb_total;        // K blocks of 64 in all
     int kb_per_split;    // K blocks per CTA of a cluster
     int splits;
+    int grid_x;          // blocks (clusters when K is split) that share the tiles
+    int tma_store;       // the output goes through shared memory and a TMA store / reduce
+    int glu_kind;        // gated mode: 0 silu, 1 tanh gelu
     int* err;
 };
 
+// Tokens staged per TMA store: the box height of the output's tensor map.
+__host__ __device__ constexpr int sub_rows(int bn) { return (bn == 16 || bn == 64) ? 16 : 32; }
+
 template <int BN> struct TcCfg {
-    static constexpr int STAGES = BN <= 16 ? 6 : (BN <= 32 ? 5 : 4);
+    // two blocks share an SM up to BN = 64 (each may use about 113 KB of shared memory)
+    static constexpr int STAGES = BN <= 16 ? 5 : (BN == 128 ? 5 : 4);
     static constexpr int B_BYTES = BN * TC_BK * 2;
-    static constexpr int COLS = BN < 32 ? 32 : BN;                 // TMEM columns: a power of two >= 32
-    static constexpr int SMEM = 1024 + STAGES * (A_BYTES + B_BYTES) + 256;
+    static constexpr int ACC_COLS = BN;                            // columns of one accumulator
+    static constexpr int COLS = 2 * BN < 32 ? 32 : 2 * BN;         // two accumulators: a power of two >= 32
+    static constexpr int SUB = sub_rows(BN);                       // tokens staged per TMA store
+    static constexpr int STAGING = SUB * TC_BM * 4;
+    static constexpr int SMEM = 1024 + STAGES * (A_BYTES + B_BYTES) + STAGING + 256;
 };
 
+__device__ __forceinline__ void grid_dependents_may_launch() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Persistent: block b works on tiles b, b + gridDim.x, ...  The accumulator in tensor memory is
+// double-buffered, so the epilogue of one tile runs while the next tile's products are issued.
 template <int BN, int MODE>
-__global__ void __launch_bounds__(TC_THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, TcArgs a) {
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+               const __grid_constant__ CUtensorMap tmap_y, TcArgs a) {
     using C = TcCfg<BN>;
     constexpr int STAGES = C::STAGES;
+    constexpr bool GLU = MODE == OUT_BF16_GLU;
+    constexpr int OUT_COLS = GLU ? TC_BM / 2 : TC_BM;              // output features of a tile
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (base - raw);
     const uint32_t a_base = base;
     const uint32_t b_base = base + STAGES * A_BYTES;
-    const uint32_t bar_base = b_base + STAGES * C::B_BYTES;
-    // barriers: full[STAGES], empty[STAGES], accum; then the TMEM address and the abort flag
-    const uint32_t full0 = bar_base, empty0 = bar_base + 8 * STAGES, accum_bar = bar_base + 16 * STAGES;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + (bar_base - base) + 16 * STAGES + 8);
+    const uint32_t stage_out = b_base + STAGES * C::B_BYTES;        // the output sub-tile on its way to TMA
+    const uint32_t bar_base = stage_out + C::STAGING;
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the TMEM address and the abort flag
+    const uint32_t full0 = bar_base, empty0 = bar_base + 8 * STAGES;
+    const uint32_t acc_full0 = bar_base + 16 * STAGES, acc_empty0 = acc_full0 + 16;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + (bar_base - base) + 16 * STAGES + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-    float* partial = reinterpret_cast<float*>(smem);           // reused after the main loop: [BN][128] floats
+    float* partial = reinterpret_cast<float*>(smem);   // split-K only (one tile per block): [BN][128] floats
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * TC_BM;
-    const int tok0 = blockIdx.y * BN;
     const uint32_t rank = a.splits > 1 ? cluster_rank() : 0u;
     const int kb0 = (int)rank * a.kb_per_split;
     int n_kb = a.kb_total - kb0;
     if (n_kb > a.kb_per_split) n_kb = a.kb_per_split;
     if (n_kb < 0) n_kb = 0;
+    const int tok_tiles = (a.T + BN - 1) / BN;
+    const int n_tiles = ((a.N + TC_BM - 1) / TC_BM) * tok_tiles;
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_w);
         prefetch_tmap(&tmap_x);
+        if (a.tma_store) prefetch_tmap(&tmap_y);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 4);
+        }
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -101,28 +133,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    grid_dependents_may_launch();
+    bool first_cluster_barrier_done = false;
 
-    bool ok = true;
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, a.err, ERR_WAIT_EMPTY)) break;
-                mbar_expect_tx(full0 + 8 * s, A_BYTES + C::B_BYTES);
-                tma_load_2d(a_base + s * A_BYTES, &tmap_w, full0 + 8 * s, (kb0 + kb) * TC_BK, row0);
-                tma_load_2d(b_base + s * C::B_BYTES, &tmap_x, full0 + 8 * s, (kb0 + kb) * TC_BK, tok0);
-                ++issued;
+            // weights do not depend on the kernel before this one: their first tiles are
+            // requested before waiting for it, the tokens' tiles after
+            int pre = 0;
+            if ((int)blockIdx.x < n_tiles) {
+                const int row0 = ((int)blockIdx.x / tok_tiles) * TC_BM;
+                pre = n_kb < STAGES ? n_kb : STAGES;
+                for (int kb = 0; kb < pre; ++kb) {
+                    mbar_expect_tx(full0 + 8 * kb, A_BYTES + C::B_BYTES);
+                    tma_load_2d(a_base + kb * A_BYTES, &tmap_w, full0 + 8 * kb, (kb0 + kb) * TC_BK, row0);
+                }
+            }
+            grid_dependency_wait();
+            int it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+                const int row0 = (tile / tok_tiles) * TC_BM, tok0 = (tile % tok_tiles) * BN;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= pre) {
+                        if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1u, abort_flag, a.err, ERR_WAIT_EMPTY)) {
+                            alive = false;
+                            break;
+                        }
+                        mbar_expect_tx(full0 + 8 * s, A_BYTES + C::B_BYTES);
+                        tma_load_2d(a_base + s * A_BYTES, &tmap_w, full0 + 8 * s, (kb0 + kb) * TC_BK, row0);
+                    }
+                    tma_load_2d(b_base + s * C::B_BYTES, &tmap_x, full0 + 8 * s, (kb0 + kb) * TC_BK, tok0);
+                }
             }
             if (*abort_flag) {
                 // give copies that are still in flight time to land before shared memory is given up
+                const int issued = it > pre ? it : pre;
                 const int first = issued > STAGES ? issued - STAGES : 0;
-                for (int kb = first; kb < issued; ++kb) {
+                for (int k = first; k < issued; ++k) {
                     bool landed = false;
                     for (uint32_t i = 0; i < WAIT_POLLS && !landed; ++i)
-                        landed = mbar_try_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1);
+                        landed = mbar_try_wait(full0 + 8 * (k % STAGES), (k / STAGES) & 1);
                     if (!landed && a.err) atomicCAS(a.err, 0, ERR_WAIT_DRAIN);
                 }
             }
@@ -132,97 +185,191 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         // ------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_bf16(TC_BM, BN);
-            for (int kb = 0; kb < n_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!mbar_wait(full0 + 8 * s, ph, abort_flag, a.err, ERR_WAIT_FULL)) break;
+            int it = 0, local = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
+                const int ab = local & 1;
+                // the epilogue must have emptied this accumulator (two tiles ago)
+                if (!mbar_wait(acc_empty0 + 8 * ab, ((local >> 1) & 1) ^ 1u, abort_flag, a.err, ERR_WAIT_ACCUM)) break;
                 tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + ab * C::ACC_COLS;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, abort_flag, a.err, ERR_WAIT_FULL)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
 #pragma unroll
-                for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
-                    const uint64_t da = smem_desc_sw128(a_base + s * A_BYTES + k * TC_UMMA_K * 2);
-                    const uint64_t db = smem_desc_sw128(b_base + s * C::B_BYTES + k * TC_UMMA_K * 2);
-                    umma_bf16(tmem_base, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
+                        const uint64_t da = smem_desc_sw128(a_base + s * A_BYTES + k * TC_UMMA_K * 2);
+                        const uint64_t db = smem_desc_sw128(b_base + s * C::B_BYTES + k * TC_UMMA_K * 2);
+                        umma_bf16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);
                 }
-                umma_commit(empty0 + 8 * s);
+                umma_commit(acc_full0 + 8 * ab);
             }
-            umma_commit(accum_bar);
         }
         __syncwarp();
     } else {
-        // ----------------------------------- epilogue warps wait for the accumulator
-        ok = n_kb == 0 || mbar_wait(accum_bar, 0, abort_flag, a.err, ERR_WAIT_ACCUM);
-        ok = __all_sync(0xffffffffu, ok);
-        tc_fence_after_sync();
-    }
-
-    const int q = warp & 3;                     // TMEM lane quarter this warp may read
-    const int f_local = q * 32 + lane;
-    const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-
-    if (a.splits > 1) {
-        if (warp >= 2 && rank != 0) {
-            // partial accumulators of the other ranks go to their own shared memory
+        // ---------------------------------------------------------------- epilogue
+        grid_dependency_wait();                     // the output may still be read by the kernel before this one
+        const int q = warp & 3;                     // TMEM lane quarter this warp may read
+        const int f_local = q * 32 + lane;
+        const bool writer = !GLU || (lane & 1) == 0;
+        const int col = GLU ? f_local >> 1 : f_local;
+        float* stage_f = reinterpret_cast<float*>(smem + (stage_out - base));
+        __nv_bfloat16* stage_h = reinterpret_cast<__nv_bfloat16*>(stage_f);
+        const uint32_t part_addr = smem_u32(partial);
+        int local = 0;
+        if (a.splits > 1) {
+            // ---- K is split over the cluster: one tile per block.  Every rank parks its partial
+            // accumulator in its own shared memory; then rank r sums, in rank order, a slice of the
+            // tile's token columns over all ranks and writes that slice.
+            const int tile = blockIdx.x;
+            const int row0 = (tile / tok_tiles) * TC_BM, tok0 = (tile % tok_tiles) * BN;
+            if (n_kb > 0) mbar_wait(acc_full0, 0, abort_flag, a.err, ERR_WAIT_ACCUM);
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            const bool good = *abort_flag == 0;
+            tc_fence_after_sync();
+            const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+            if (good) {
 #pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
-                uint32_t v[16];
-                if (ok && n_kb > 0) {
+                for (int c = 0; c < BN / 16; ++c) {
+                    uint32_t v[16];
                     tmem_ld16(t_lane + c * 16, v);
                     tmem_ld_wait();
-                } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0u;
+                    for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * TC_BM + f_local] = __uint_as_float(v[j]);
                 }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * TC_BM + f_local] = __uint_as_float(v[j]);
             }
-        }
-        cluster_sync();
-    }
+            cluster_sync_arrive_wait();
+            first_cluster_barrier_done = true;
+            const int f = row0 + f_local;
+            float bias_v = 0.f;
+            if (!GLU && a.bias != nullptr && f < a.N)
+                bias_v = a.bias_dtype == ZLM_F32 ? reinterpret_cast<const float*>(a.bias)[f]
+                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
+            const int out_f = GLU ? f >> 1 : f;
+            const int out_n = GLU ? a.N >> 1 : a.N;
+            const int per = (BN + a.splits - 1) / a.splits;
+            const int c_lo = (int)rank * per, c_hi = min(BN, c_lo + per);
+            uint32_t remote[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) remote[r] = r < a.splits ? map_to_rank(part_addr, (uint32_t)r) : 0u;
+            for (int cc = c_lo; cc < c_hi && good; ++cc) {
+                const int tok = tok0 + cc;
+                if (tok >= a.T) break;
+                float part[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+                    part[r] = r < a.splits ? ld_cluster_f32(remote[r] + 4u * (cc * TC_BM + f_local)) : 0.f;
+                float val = part[0];
+#pragma unroll
+                for (int r = 1; r < 8; ++r) val += part[r];
+                val += bias_v;
+                if (GLU) {
+                    const float up = __shfl_down_sync(0xffffffffu, val, 1);
+                    const float g = val;
+                    if (a.glu_kind == 0) val = __fdividef(g, 1.0f + __expf(-g));
+                    else val = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+                    val *= up;
+                }
+                if (writer && out_f < out_n) {
+                    if (MODE == OUT_BF16 || MODE == OUT_BF16_GLU)
+                        reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
+                    else if (MODE == OUT_F32_ACC)       // one adder per element: the order is fixed
+                        atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
+                    else
+                        reinterpret_cast<float*>(a.Y)[(long)tok * a.ldy + out_f] = val;
+                }
+            }
+        } else
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int row0 = (tile / tok_tiles) * TC_BM, tok0 = (tile % tok_tiles) * BN;
+            const int ab = local & 1;
+            if (n_kb > 0) mbar_wait(acc_full0 + 8 * ab, (local >> 1) & 1, abort_flag, a.err, ERR_WAIT_ACCUM);
+            asm volatile("bar.sync 2, 128;" ::: "memory");     // the four warps go on together or not at all
+            if (*abort_flag) break;
+            tc_fence_after_sync();
+            const uint32_t t_lane = tmem_base + ab * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
 
-    if (warp >= 2 && rank == 0 && ok) {
-        const int f = row0 + f_local;
-        float bias_v = 0.f;
-        if (a.bias != nullptr && f < a.N)
-            bias_v = a.bias_dtype == ZLM_F32 ? reinterpret_cast<const float*>(a.bias)[f]
-                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
-        const uint32_t part_addr = smem_u32(partial);
+            const int f = row0 + f_local;
+            float bias_v = 0.f;
+            if (!GLU && a.bias != nullptr && f < a.N)
+                bias_v = a.bias_dtype == ZLM_F32 ? reinterpret_cast<const float*>(a.bias)[f]
+                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
+            const int out_f = GLU ? f >> 1 : f;
+            const int out_n = GLU ? a.N >> 1 : a.N;
 #pragma unroll 1
-        for (int c = 0; c < BN / 16; ++c) {
-            if (tok0 + c * 16 >= a.T) break;            // whole chunk beyond the last token (uniform per warp)
-            uint32_t v[16];
-            if (n_kb > 0) {
+            for (int c = 0; c < BN / 16; ++c) {
+                if (tok0 + c * 16 >= a.T) break;            // whole chunk beyond the last token (uniform per block)
+                const int sub_row = (c * 16) % C::SUB;       // row of this chunk inside the staged sub-tile
+                if (a.tma_store && sub_row == 0 && (c > 0 || local > 0)) {
+                    // the previous sub-tile must have left shared memory before it is overwritten
+                    if (warp == 2 && lane == 0) tma_store_wait_read();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+                uint32_t v[16];
                 tmem_ld16(t_lane + c * 16, v);
                 tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] = 0u;
-            }
-            for (uint32_t r = 1; r < (uint32_t)a.splits; ++r) {
-                const uint32_t remote = map_to_rank(part_addr, r);
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    v[j] = __float_as_uint(__uint_as_float(v[j]) +
-                                           ld_cluster_f32(remote + 4u * ((c * 16 + j) * TC_BM + f_local)));
-            }
-            if (f < a.N) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const int tok = tok0 + c * 16 + j;
-                    if (tok < a.T) {
-                        const float val = __uint_as_float(v[j]) + bias_v;
-                        if (MODE == OUT_BF16) {
-                            reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + f] = __float2bfloat16_rn(val);
-                        } else {
-                            float* dst = reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + f;
-                            *dst = MODE == OUT_F32_ACC ? *dst + val : val;
+                    float val = __uint_as_float(v[j]) + bias_v;
+                    if (GLU) {
+                        // even lanes hold a gate row, the next lane the matching up row
+                        const float up = __shfl_down_sync(0xffffffffu, val, 1);
+                        const float g = val;
+                        if (a.glu_kind == 0) val = __fdividef(g, 1.0f + __expf(-g));
+                        else val = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+                        val *= up;
+                    }
+                    if (a.tma_store) {
+                        if (writer) {
+                            if (MODE == OUT_F32 || MODE == OUT_F32_ACC) stage_f[(sub_row + j) * OUT_COLS + col] = val;
+                            else stage_h[(sub_row + j) * OUT_COLS + col] = __float2bfloat16_rn(val);
+                        }
+                    } else {
+                        const int tok = tok0 + c * 16 + j;
+                        if (writer && tok < a.T && out_f < out_n) {
+                            if (MODE == OUT_BF16 || MODE == OUT_BF16_GLU)
+                                reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
+                            else if (MODE == OUT_F32_ACC)   // one adder per element: the order is fixed
+                                atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
+                            else
+                                reinterpret_cast<float*>(a.Y)[(long)tok * a.ldy + out_f] = val;
                         }
                     }
                 }
+                const bool last_of_sub = sub_row + 16 == C::SUB || c == BN / 16 - 1 || tok0 + (c + 1) * 16 >= a.T;
+                if (a.tma_store && last_of_sub) {
+                    fence_proxy_async();                    // the staged rows become visible to the TMA engine
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (warp == 2 && lane == 0) {
+                        const int x = GLU ? row0 >> 1 : row0;
+                        const int y = tok0 + c * 16 - sub_row;
+                        if (MODE == OUT_F32_ACC) tma_reduce_add_2d(&tmap_y, stage_out, x, y);
+                        else tma_store_2d(&tmap_y, stage_out, x, y);
+                        tma_store_commit();
+                    }
+                }
             }
+            // this accumulator may be overwritten by the tile after next
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * ab);
         }
+        if (a.tma_store && a.splits == 1 && warp == 2 && lane == 0) tma_store_wait_read();
+        __syncwarp();
     }
 
-    if (a.splits > 1) cluster_sync();            // the other ranks keep their shared memory until rank 0 has read it
+    if (a.splits > 1) {
+        // every thread of every rank passes two cluster barriers: after the partials are written
+        // (rank 0's epilogue passes the first one inside its loop) and after they are read
+        if (!first_cluster_barrier_done) cluster_sync_arrive_wait();
+        cluster_sync_arrive_wait();
+    }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -249,24 +396,30 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// A bf16 matrix [rows, cols] with row stride ld (elements), read in boxes of box_rows x 64.
-static int make_map(CUtensorMap* m, const void* ptr, long rows, long cols, long ld, int box_rows) {
+// A matrix [rows, cols] with row stride ld (elements).  Operands (bf16) are read in boxes of box_rows x 64
+// with the 128-byte swizzle; outputs (kind 1 bf16, 2 float) are written in boxes of box_rows x box_cols, unswizzled.
+static int make_map(CUtensorMap* m, const void* ptr, long rows, long cols, long ld, int box_rows, int box_cols,
+                    int kind) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return ZLM_ERR_UNSUPPORTED;
+    const int es = kind == 2 ? 4 : 2;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * es};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    CUresult r = fn(m, kind == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    kind == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : ZLM_ERR_BAD_ARG;
 }
 
 struct MapKey {
-    const void* ptr; long rows, cols, ld; int box;
+    const void* ptr; long rows, cols, ld; int box, box_cols, kind;
     bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box;
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box == o.box &&
+               box_cols == o.box_cols && kind == o.kind;
     }
 };
 struct MapKeyHash {
@@ -274,20 +427,22 @@ struct MapKeyHash {
         size_t h = std::hash<const void*>()(k.ptr);
         h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols;
         h = h * 1000003u ^ (size_t)k.ld; h = h * 1000003u ^ (size_t)k.box;
+        h = h * 1000003u ^ (size_t)(k.box_cols * 4 + k.kind);
         return h;
     }
 };
 
 // Descriptors depend on (address, shape, box) only, so they are built once and kept.
-static int cached_map(CUtensorMap* out, const void* ptr, long rows, long cols, long ld, int box) {
+static int cached_map(CUtensorMap* out, const void* ptr, long rows, long cols, long ld, int box,
+                      int box_cols = TC_BK, int kind = 0) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
-    MapKey k{ptr, rows, cols, ld, box};
+    MapKey k{ptr, rows, cols, ld, box, box_cols, kind};
     auto it = cache.find(k);
     if (it == cache.end()) {
         CUtensorMap m;
-        int rc = make_map(&m, ptr, rows, cols, ld, box);
+        int rc = make_map(&m, ptr, rows, cols, ld, box, box_cols, kind);
         if (rc) return rc;
         if (cache.size() > 65536) cache.clear();
         it = cache.emplace(k, m).first;
@@ -307,7 +462,8 @@ static int* error_word() {
 }
 
 template <int BN, int MODE>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, const TcArgs& a,
+                     cudaStream_t stream) {
     using C = TcCfg<BN>;
     static bool configured = false;
     if (!configured) {
@@ -317,27 +473,38 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs&
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((a.N + TC_BM - 1) / TC_BM, (a.T + BN - 1) / BN, a.splits);
+    cfg.gridDim = dim3(a.grid_x, 1, a.splits);
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = C::SMEM;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = a.splits;
-    cfg.attrs = attr;
-    cfg.numAttrs = a.splits > 1 ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, MODE>, mw, mx, a);
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start while its predecessor drains
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = a.splits;
+    static const bool no_pdl = getenv("ZLM_NO_PDL") != nullptr;
+    if (no_pdl) {
+        attr[0] = attr[1];
+        cfg.attrs = attr;
+        cfg.numAttrs = a.splits > 1 ? 1 : 0;
+    } else {
+        cfg.attrs = attr;
+        cfg.numAttrs = a.splits > 1 ? 2 : 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, MODE>, mw, mx, my, a);
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 template <int BN>
-static int pick_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, cudaStream_t s) {
+static int pick_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, const TcArgs& a,
+                     cudaStream_t s) {
     switch (mode) {
-        case OUT_F32: return launch_tc<BN, OUT_F32>(mw, mx, a, s);
-        case OUT_F32_ACC: return launch_tc<BN, OUT_F32_ACC>(mw, mx, a, s);
-        default: return launch_tc<BN, OUT_BF16>(mw, mx, a, s);
+        case OUT_F32: return launch_tc<BN, OUT_F32>(mw, mx, my, a, s);
+        case OUT_F32_ACC: return launch_tc<BN, OUT_F32_ACC>(mw, mx, my, a, s);
+        case OUT_BF16_GLU: return launch_tc<BN, OUT_BF16_GLU>(mw, mx, my, a, s);
+        default: return launch_tc<BN, OUT_BF16>(mw, mx, my, a, s);
     }
 }
 
@@ -346,19 +513,25 @@ static int pick_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, con
 using namespace zlm;
 
 // X: bf16 [T, K] (row stride ldx), W: bf16 [N, K] (row stride ldw), Y: float or bf16 [T, N] (row stride ldy).
+// glu: 0 = plain product; 1 / 2 = the rows of W alternate gate and up rows and Y is bf16 [T, N/2] holding
+//      silu(gate) * up (1) or tanh-gelu(gate) * up (2).
 // splits: 0 = choose, else the number of CTAs a tile's K range is split over (1..8).
-// Refuses (ZLM_ERR_UNSUPPORTED) strides or addresses TMA cannot take; the caller falls back.
+// Refuses (ZLM_ERR_UNSUPPORTED) strides or addresses TMA cannot read; the caller falls back.
 ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
-                           int accumulate, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
+                           int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
                            cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
-    if (K <= 0 || ldx < K || ldw < K || ldy < N || splits < 0 || splits > 8) return ZLM_ERR_BAD_ARG;
+    const int n_out = glu ? N / 2 : N;
+    if (K <= 0 || ldx < K || ldw < K || ldy < n_out || splits < 0 || splits > 8 || glu < 0 || glu > 2)
+        return ZLM_ERR_BAD_ARG;
     if (accumulate && y_dtype != ZLM_F32) return ZLM_ERR_BAD_ARG;
+    if (glu && ((N & 1) || y_dtype != ZLM_BF16 || bias != nullptr)) return ZLM_ERR_BAD_ARG;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return ZLM_ERR_UNSUPPORTED;
     const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
     TcArgs a;
     a.bias = bias; a.bias_dtype = bias_dtype; a.Y = Y; a.ldy = ldy; a.T = T; a.N = N; a.K = K;
     a.kb_total = (K + TC_BK - 1) / TC_BK;
+    a.glu_kind = glu == 2 ? 1 : 0;
     a.err = error_word();
     const int tiles = ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
     int s = splits;
@@ -376,18 +549,38 @@ ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int b
     a.kb_per_split = (a.kb_total + s - 1) / s;
     s = (a.kb_total + a.kb_per_split - 1) / a.kb_per_split;   // every rank gets at least one block
     a.splits = s;
-    CUtensorMap mw, mx;
+    // one tile per block when K is split; otherwise as many blocks as fit the GPU share the tiles
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+            sm_count = 148;
+    }
+    const int per_sm = bn <= 64 ? 2 : 1;
+    a.grid_x = (s > 1 || tiles < sm_count * per_sm) ? tiles : sm_count * per_sm;
+    CUtensorMap mw, mx, my;
     int rc = cached_map(&mw, W, N, K, ldw, TC_BM);
     if (rc) return rc;
     rc = cached_map(&mx, X, T, K, ldx, bn);
     if (rc) return rc;
-    const int mode = y_dtype == ZLM_BF16 ? OUT_BF16 : (accumulate ? OUT_F32_ACC : OUT_F32);
+    const int mode = glu ? OUT_BF16_GLU : (y_dtype == ZLM_BF16 ? OUT_BF16 : (accumulate ? OUT_F32_ACC : OUT_F32));
+    // the output goes through TMA when its rows start on 16-byte boundaries; else the threads store directly
+    const int es = y_dtype == ZLM_BF16 ? 2 : 4;
+    static const bool no_tma_store = getenv("ZLM_NO_TMA_STORE") != nullptr;
+    a.tma_store = ((uintptr_t)Y % 16 == 0) && ((ldy * es) % 16 == 0) && !no_tma_store;
+    if (a.tma_store) {
+        rc = cached_map(&my, Y, T, n_out, ldy, sub_rows(bn), glu ? TC_BM / 2 : TC_BM, es == 2 ? 1 : 2);
+        if (rc) return rc;
+    } else {
+        my = mx;                                              // never dereferenced
+    }
     switch (bn) {
-        case 16: return pick_mode<16>(mode, mw, mx, a, stream);
-        case 32: return pick_mode<32>(mode, mw, mx, a, stream);
-        case 64: return pick_mode<64>(mode, mw, mx, a, stream);
-        case 128: return pick_mode<128>(mode, mw, mx, a, stream);
-        default: return pick_mode<256>(mode, mw, mx, a, stream);
+        case 16: return pick_mode<16>(mode, mw, mx, my, a, stream);
+        case 32: return pick_mode<32>(mode, mw, mx, my, a, stream);
+        case 64: return pick_mode<64>(mode, mw, mx, my, a, stream);
+        case 128: return pick_mode<128>(mode, mw, mx, my, a, stream);
+        default: return pick_mode<256>(mode, mw, mx, my, a, stream);
     }
 }
 

@@ -52,7 +52,7 @@ _PROTOTYPES = {
         "zlm_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
         "zlm_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float,
                         c_void_p],
-        "zlm_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "zlm_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "zlm_add": [c_void_p, c_void_p, c_long, c_void_p],
         "zlm_convert": [c_void_p, c_int, c_void_p, c_int, c_long, c_void_p],
     },
@@ -75,8 +75,8 @@ _PROTOTYPES = {
         "zlm_attention_tc_status": [c_void_p],
     },
     "gemm_tc": {
-        "zlm_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_long,
-                        c_long, c_long, c_int, c_void_p],
+        "zlm_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                        c_long, c_long, c_long, c_int, c_void_p],
         "zlm_gemm_tc_status": [c_void_p],
     },
     "sampling": {
@@ -165,8 +165,9 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
            "rmsnorm")
 
 
-def gated_act(gu: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
-    """out[t, j] = act(gu[t, j]) * gu[t, I + j] for gu of shape [T, 2I]."""
+def gated_act(gu: torch.Tensor, out: torch.Tensor, activation: str = "silu", interleaved: bool = False) -> None:
+    """out[t, j] = act(gate) * up for gu of shape [T, 2I]: gate j, up j in columns (j, I + j), or in columns
+    (2j, 2j + 1) when ``interleaved``."""
     _cuda(gu, "gu"); _cuda(out, "out", gu.dtype)
     T, I = out.shape
     if gu.shape != (T, 2 * I):
@@ -174,8 +175,8 @@ def gated_act(gu: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> 
     kind = {"silu": 0, "gelu_tanh": 1}.get(activation)
     if kind is None:
         raise KernelError(f"gated_act: activation {activation!r} is not known (silu, gelu_tanh)")
-    _check(_fn("elementwise", "zlm_gated_act")(gu.data_ptr(), out.data_ptr(), code(gu.dtype), T, I, kind, _stream()),
-           "gated_act")
+    _check(_fn("elementwise", "zlm_gated_act")(gu.data_ptr(), out.data_ptr(), code(gu.dtype), T, I, kind,
+                                               int(interleaved), _stream()), "gated_act")
 
 
 def add_(y: torch.Tensor, x: torch.Tensor) -> None:
@@ -390,9 +391,15 @@ def fast_gemm_libraries():
     return ("gemm_tc",)
 
 
+GLU_KINDS = {"silu": 1, "gelu_tanh": 2}
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, splits: int = 0) -> bool:
+            accumulate: bool = False, splits: int = 0, glu: Optional[str] = None) -> bool:
     """out[T,N] (+)= x[T,K] @ w[N,K]^T (+ bias) on the tcgen05 tensor cores, bf16 operands.
+
+    With ``glu`` ("silu" or "gelu_tanh") the rows of w alternate gate and up rows and out is bf16 [T, N/2]
+    holding act(gate) * up.
 
     Returns False, having done nothing, if the operands are not what TMA can read (a row stride that is no
     multiple of 8 elements, a base address off a 16-byte boundary).
@@ -406,7 +413,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
         raise KernelError("gemm_tc: x and w must be bfloat16")
     T, K = x.shape
     N = w.shape[0]
-    if w.shape[1] != K or out.shape != (T, N):
+    n_out = N // 2 if glu else N
+    if glu and (glu not in GLU_KINDS or N % 2 or out.dtype != torch.bfloat16 or bias is not None):
+        raise KernelError("gemm_tc: the gated mode needs silu or gelu_tanh, an even row count, a bf16 output, no bias")
+    if w.shape[1] != K or out.shape != (T, n_out):
         raise KernelError(f"gemm: shapes do not match: x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     if accumulate and out.dtype != torch.float32:
         raise KernelError("gemm: accumulation needs a float32 output")
@@ -416,8 +426,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
             raise KernelError("gemm: bias length does not match")
     status = _fn("gemm_tc", "zlm_gemm_tc")(
         x.data_ptr(), w.data_ptr(), _ptr(bias), code(bias.dtype) if bias is not None else F32, out.data_ptr(),
-        code(out.dtype), int(accumulate), T, N, K, x.stride(0) if T > 1 else K, w.stride(0) if N > 1 else K,
-        out.stride(0) if T > 1 else N, int(splits), _stream())
+        code(out.dtype), int(accumulate), GLU_KINDS[glu] if glu else 0, T, N, K, x.stride(0) if T > 1 else K,
+        w.stride(0) if N > 1 else K, out.stride(0) if T > 1 else n_out, int(splits), _stream())
     if status == -2:
         return False
     _check(status, "gemm_tc")

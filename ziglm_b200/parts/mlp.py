@@ -5,7 +5,9 @@ silu(z) = z/(1+exp(-z)), f = W_d act, no biases (src/model.zig:725-745,
 src/math.zig:1108-1117); its GPU path applies the tanh GELU to every
 architecture (src/cuda_model.zig:695,1379), which is not reproduced.  Gate and
 up are one matrix product over the concatenated weight [gate; up]; the
-activation is a parameter of the part.
+activation is a parameter of the part.  On the bfloat16 path the rows of that
+weight alternate gate and up rows, so that the product's epilogue can apply the
+activation and write act(gate) * up directly.
 """
 from __future__ import annotations
 
@@ -27,6 +29,7 @@ class GatedMLP(Part):
         if spec.bias:
             raise ValueError("gated_mlp: biases are not supported")
         self.intermediate = spec.intermediate
+        self.interleaved = False
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
@@ -39,7 +42,11 @@ class GatedMLP(Part):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors["gate.weight"], tensors["up.weight"]
         wide = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
-        self.gate_up = Linear(torch.cat([g.to(wide), u.to(wide)], dim=0))
+        self.interleaved = self.dtype == torch.bfloat16 and wide == torch.bfloat16
+        if self.interleaved:
+            self.gate_up = Linear(torch.stack([g, u], dim=1).reshape(2 * self.intermediate, -1))
+        else:
+            self.gate_up = Linear(torch.cat([g.to(wide), u.to(wide)], dim=0))
         self.down = Linear(tensors["down.weight"])
 
     def kernel_libraries(self) -> Tuple[str, ...]:
@@ -51,10 +58,12 @@ class GatedMLP(Part):
 
     def forward(self, step, h: torch.Tensor, residual: torch.Tensor) -> None:
         T = h.shape[0]
-        gu = step.ws.buf("gate_up", (T, 2 * self.intermediate), self.dtype)
-        self.gate_up(h, gu)
         act = step.ws.buf("ffn_act", (T, self.intermediate), self.dtype)
-        kernels.gated_act(gu, act, self.spec.activation)
+        fused = self.interleaved and kernels.gemm_tc(h, self.gate_up.weight, act, glu=self.spec.activation)
+        if not fused:
+            gu = step.ws.buf("gate_up", (T, 2 * self.intermediate), self.dtype)
+            self.gate_up(h, gu)
+            kernels.gated_act(gu, act, self.spec.activation, interleaved=self.interleaved)
         self.down(act, residual, accumulate=True)
 
 
