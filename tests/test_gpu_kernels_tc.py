@@ -1,0 +1,188 @@
+"""The tensor-core kernels alone (tcgen05/TMA matrix product, paged attention for prompts and for decode
+steps) against plain float32 statements of the same operations, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as P
+from test_gpu_kernels import DEV, dense_attention_case, paged, plain_attention_rows, rnd
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def K():
+    from ziglm_b200 import kernels
+    return kernels
+
+
+def ref_product(x, w, b=None):
+    return P.linear(x.float(), w, b)
+
+
+# every token-tile width (16..256), one tile and many, K with a ragged tail, N that is no multiple of 128
+@pytest.mark.parametrize("T,N,K_", [(1, 331, 120), (8, 256, 512), (16, 128, 64), (17, 1000, 264), (45, 128, 64),
+                                    (64, 4096, 1024), (70, 352, 64), (128, 20000, 192), (300, 1000, 4096),
+                                    (1000, 40000, 128)])
+@pytest.mark.parametrize("out_dtype", [BF, torch.float32])
+def test_gemm_tc_shapes(K, T, N, K_, out_dtype):
+    x, w, b = rnd((T, K_), BF, seed=1), rnd((N, K_), BF, 0.05, seed=2), rnd((N,), BF, seed=3)
+    want = ref_product(x, w, b)
+    out = torch.full((T, N), 7.0, dtype=out_dtype, device=DEV)
+    assert K.gemm_tc(x.to(DEV), w.to(DEV), out, bias=b.to(DEV))
+    torch.cuda.synchronize()
+    assert K.gemm_tc_status() == 0
+    tol = dict(atol=1e-3, rtol=1e-3) if out_dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+    assert torch.allclose(out.float().cpu(), want, **tol)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("T", [1, 8, 33, 64])
+def test_gemm_tc_split_k_is_exact_in_order(K, splits, T):
+    """K split over the CTAs of a cluster: same result whatever the number of splits, up to the order of float sums;
+    and the same bits every time."""
+    x, w = rnd((T, 2048), BF, seed=4), rnd((256, 2048), BF, 0.05, seed=5)
+    base = rnd((T, 256), torch.float32, seed=6)
+    out = base.to(DEV).clone()
+    assert K.gemm_tc(x.to(DEV), w.to(DEV), out, accumulate=True, splits=splits)
+    again = base.to(DEV).clone()
+    assert K.gemm_tc(x.to(DEV), w.to(DEV), again, accumulate=True, splits=splits)
+    torch.cuda.synchronize()
+    assert K.gemm_tc_status() == 0
+    assert torch.equal(out, again)
+    assert torch.allclose(out.cpu(), base + ref_product(x, w), atol=2e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("kind", ["silu", "gelu_tanh"])
+@pytest.mark.parametrize("T,N,K_,splits", [(8, 512, 256, 0), (45, 352, 64, 0), (100, 400, 120, 0), (8, 1024, 2048, 4),
+                                           (600, 3000, 512, 0)])
+def test_gemm_tc_gated(K, kind, T, N, K_, splits):
+    x, w = rnd((T, K_), BF, seed=7), rnd((N, K_), BF, 0.05, seed=8)
+    gu = ref_product(x, w)
+    g, u = gu[:, 0::2], gu[:, 1::2]
+    want = (P.silu(g) if kind == "silu" else torch.nn.functional.gelu(g, approximate="tanh")) * u
+    out = torch.full((T, N // 2), 7.0, dtype=BF, device=DEV)
+    assert K.gemm_tc(x.to(DEV), w.to(DEV), out, glu=kind, splits=splits)
+    torch.cuda.synchronize()
+    assert K.gemm_tc_status() == 0
+    assert torch.allclose(out.float().cpu(), want, atol=3e-2, rtol=2e-2)
+
+
+def test_gemm_tc_rows_of_wider_buffers_and_odd_output_stride(K):
+    xb = rnd((20, 300), BF, seed=9).to(DEV)
+    x = xb[:, 40:168]                                     # row stride 300 is no multiple of 8: refused
+    w = rnd((50, 128), BF, 0.05, seed=10).to(DEV)
+    out = torch.empty(20, 50, dtype=torch.float32, device=DEV)
+    assert K.gemm_tc(x, w, out) is False
+    xb = rnd((20, 304), BF, seed=9).to(DEV)
+    x = xb[:, 40:168]
+    assert K.gemm_tc(x, w, out) is True                   # output rows of 50 floats: stored by the threads
+    assert torch.allclose(out.cpu(), ref_product(x.cpu(), w.cpu()), atol=1e-3, rtol=1e-3)
+    wide = torch.zeros(20, 64, dtype=torch.float32, device=DEV)
+    assert K.gemm_tc(x, w, wide[:, :50], accumulate=True)  # output rows inside a wider buffer: through TMA
+    assert torch.allclose(wide[:, :50].cpu(), ref_product(x.cpu(), w.cpu()), atol=1e-3, rtol=1e-3)
+    assert (wide[:, 50:] == 0).all()
+    assert K.gemm_tc_status() == 0
+    with pytest.raises(K.KernelError):
+        K.gemm_tc(x.float(), w, out)
+
+
+# ------------------------------------------------------------------ attention
+def run_decode(K, nh, nkv, hd, lens_past, window, n_splits, seed=20):
+    lens_new = [1] * len(lens_past)
+    ks, vs, q, positions, seq = dense_attention_case(BF, nh, nkv, hd, lens_past, lens_new, seed=seed)
+    kp, vp, table = paged(ks, vs, 64, BF, seed=2)
+    T = q.shape[0]
+    out = torch.zeros(T, nh * hd, dtype=BF, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    wide = torch.zeros(T, nh * hd + 64, dtype=BF)
+    wide[:, :nh * hd] = q.reshape(T, nh * hd)
+    po = torch.empty(T * nh * n_splits * hd, device=DEV)
+    pm = torch.empty(T * nh * n_splits * 2, device=DEV)
+    assert K.attention_decode(wide.to(DEV), out, nh, nkv, hd, scale, window,
+                              torch.tensor(positions, dtype=torch.int32, device=DEV),
+                              torch.tensor(seq, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV), vp.to(DEV),
+                              64, n_splits, po, pm)
+    torch.cuda.synchronize()
+    assert K.attention_tc_status() == 0
+    want = plain_attention_rows(ks, vs, q, positions, seq, scale, window)
+    return out.float().cpu().view(T, nh, hd), want
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (4, 4), (16, 1), (6, 3)])
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_attention_decode(K, hd, nh, nkv, window, n_splits):
+    got, want = run_decode(K, nh, nkv, hd, [0, 130, 63, 300, 64], window, n_splits)
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (4, 4), (16, 1)])
+@pytest.mark.parametrize("window", [None, 37, 100])
+def test_attention_prefill(K, hd, nh, nkv, window):
+    lens_past, lens_new = [0, 130, 63, 0, 5], [21, 1, 70, 200, 64]
+    ks, vs, q, positions, seq = dense_attention_case(BF, nh, nkv, hd, lens_past, lens_new, seed=30)
+    kp, vp, table = paged(ks, vs, 64, BF, seed=3)
+    T = q.shape[0]
+    out = torch.zeros(T, nh * hd, dtype=BF, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    cu = [0]
+    for n in lens_new:
+        cu.append(cu[-1] + n)
+    assert K.attention_prefill(q.reshape(T, nh * hd).to(DEV), out, len(lens_new), max(lens_new), nh, nkv, hd, scale,
+                               window, torch.tensor(cu, dtype=torch.int32, device=DEV),
+                               torch.tensor(lens_past, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV),
+                               vp.to(DEV), 64)
+    torch.cuda.synchronize()
+    assert K.attention_tc_status() == 0
+    want = plain_attention_rows(ks, vs, q, positions, seq, scale, window)
+    assert torch.allclose(out.float().cpu().view(T, nh, hd), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_tc_attention_finds_one_far_key_and_respects_the_window_edge(K, kernel, hd):
+    """One key is made to dominate: far back among hundreds (every page position, split boundary), then just
+    inside and just outside the window.  The output must be that key's value, or must not be."""
+    nh, nkv, n = 2, 1, 700
+    scale = 1.0
+    cases = [(far, None, True) for far in (0, 3, 63, 64, 389, 640, 699)]
+    cases += [(n - 1 - 49, 50, True), (n - 1 - 50, 50, False)]
+    for far, window, visible in cases:
+        k = rnd((n, nkv, hd), BF, 0.1, seed=40)
+        v = rnd((n, nkv, hd), BF, 1.0, seed=41)
+        q = rnd((1, nh, hd), BF, 0.1, seed=42)
+        k[far] = (q[0, 0].float() * 400.0).to(BF)
+        kp, vp, table = paged([k], [v], 64, BF, seed=far)
+        out = torch.zeros(1, nh * hd, dtype=BF, device=DEV)
+        if kernel == "decode":
+            ns = 4
+            po = torch.empty(nh * ns * hd, device=DEV)
+            pm = torch.empty(nh * ns * 2, device=DEV)
+            assert K.attention_decode(q.reshape(1, -1).to(DEV), out, nh, nkv, hd, scale, window,
+                                      torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                                      torch.zeros(1, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV),
+                                      vp.to(DEV), 64, ns, po, pm)
+        else:
+            assert K.attention_prefill(q.reshape(1, -1).to(DEV), out, 1, 1, nh, nkv, hd, scale, window,
+                                       torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                                       torch.tensor([n - 1], dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV),
+                                       vp.to(DEV), 64)
+        got = out.float().cpu().view(nh, hd)
+        hit = torch.allclose(got[0], v[far, 0].float(), atol=3e-2)
+        assert hit == visible, f"{kernel} hd={hd}: key {far}, window {window}"
+        want = plain_attention_rows([k], [v], q, [n - 1], [0], scale, window)
+        assert torch.allclose(got, want[0], atol=3e-2, rtol=2e-2)
+    assert K.attention_tc_status() == 0
+
+
+def test_tc_attention_refuses_other_head_sizes(K):
+    q = torch.zeros(1, 48, dtype=BF, device=DEV)
+    out = torch.zeros(1, 48, dtype=BF, device=DEV)
+    pages = torch.zeros(1, 1, 64, 48, dtype=BF, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    assert K.attention_prefill(q, out, 1, 1, 1, 1, 48, 1.0, None, z, z, z.view(1, 2), pages, pages, 64) is False
