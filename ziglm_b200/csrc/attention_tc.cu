@@ -604,3 +604,114 @@ ZLM_EXPORT int zlm_attention_tc_status(int* out) {
     if (*out != 0) cudaMemset(w, 0, sizeof(int));
     return 0;
 }
+
+// ------------------------------------------------- decode attention that allocates nothing
+// See attention_noalloc.h: the same kernels as zlm_attention_decode, with the split scratch and the
+// error word in file-scope device arrays instead of memory the caller (or this library) allocates.
+#include "attention_noalloc.h"
+
+namespace zlm {
+
+static __device__ __align__(256) float g_noalloc_scratch[ZLM_NOALLOC_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_noalloc_err[64];
+
+struct NoAllocDevice {
+    bool ready;
+    float* scratch;
+    int* err;
+};
+static NoAllocDevice g_noalloc_dev[64];
+static std::mutex g_noalloc_mu;
+
+// In host code the arrays' names are stand-ins, not device addresses: the address that kernels may use
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+static int noalloc_setup(float** scratch, int** err) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return ZLM_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    NoAllocDevice& d = g_noalloc_dev[dev];
+    if (!d.ready) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        d.scratch = static_cast<float*>(p);
+        e = cudaGetSymbolAddress(&p, g_noalloc_err);
+        if (e != cudaSuccess) return (int)e;
+        d.err = static_cast<int*>(p);
+        d.ready = true;
+    }
+    *scratch = d.scratch;
+    *err = d.err;
+    return 0;
+}
+
+}  // namespace zlm
+
+ZLM_EXPORT int zlm_attention_decode_noalloc(const void* q, long q_row_stride, void* out, int T, int n_heads, int n_kv,
+                                            int hd, float scale, int window, const int* positions,
+                                            const int* seq_of_token, const int* block_table, int bt_stride,
+                                            const void* k_pages, const void* v_pages, long n_pages, int page_size,
+                                            int n_splits, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (n_splits < 1 || n_splits > 65535) return ZLM_ERR_BAD_ARG;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size != PAGE) return ZLM_ERR_BAD_ARG;
+    if (hd != 64 && hd != 128) return ZLM_ERR_UNSUPPORTED;
+    if (n_heads / n_kv > 16) return ZLM_ERR_UNSUPPORTED;
+    if (((uintptr_t)q % 4) || (q_row_stride % 2) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16))
+        return ZLM_ERR_UNSUPPORTED;
+    const long rows = (long)T * n_heads * n_splits;
+    if (rows * (hd + 2) > (long)ZLM_NOALLOC_SCRATCH_FLOATS) return ZLM_NOALLOC_ERR_TOO_LARGE;
+    float* scratch = nullptr;
+    int* err = nullptr;
+    int rc = noalloc_setup(&scratch, &err);
+    if (rc) return rc;
+    float* part_o = scratch;                       // [rows, hd]
+    float* part_ml = scratch + rows * hd;          // [rows, 2]
+    CUtensorMap mk, mv;
+    rc = page_map(&mk, k_pages, n_pages * n_kv * PAGE, hd);
+    if (rc) return rc;
+    rc = page_map(&mv, v_pages, n_pages * n_kv * PAGE, hd);
+    if (rc) return rc;
+    AtcCommon a;
+    a.q = (const __nv_bfloat16*)q;
+    a.q_row_stride = q_row_stride;
+    a.n_heads = n_heads;
+    a.n_kv = n_kv;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.window = window;
+    a.block_table = block_table;
+    a.bt_stride = bt_stride;
+    a.err = err;
+    dim3 grid(n_splits, n_kv, T);
+    if (hd == 128) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             DecodeCfg<128>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attn_decode_kernel<128><<<grid, ATC_THREADS, DecodeCfg<128>::SMEM, stream>>>(mk, mv, a, positions,
+                                                                                     seq_of_token, part_o, part_ml);
+        attn_merge_kernel<128><<<T * n_heads, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits);
+    } else {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             DecodeCfg<64>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attn_decode_kernel<64><<<grid, ATC_THREADS, DecodeCfg<64>::SMEM, stream>>>(mk, mv, a, positions, seq_of_token,
+                                                                                   part_o, part_ml);
+        attn_merge_kernel<64><<<T * n_heads, 64, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits);
+    }
+    return launch_status();
+}
+
+ZLM_EXPORT const char* zlm_attention_decode_noalloc_error(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case ZLM_ERR_BAD_ARG: return "bad argument (head counts, page size or number of splits)";
+        case ZLM_ERR_UNSUPPORTED: return "unsupported size (head size 64 or 128, at most 16 query heads per kv head) "
+                                         "or misaligned pointers";
+        case ZLM_NOALLOC_ERR_TOO_LARGE:
+            return "T * n_heads * n_splits * (head_dim + 2) exceeds the built-in scratch of 2 Mi floats; "
+                   "use fewer splits or zlm_attention_decode with scratch of your own";
+        default: return code > 0 ? "CUDA error (the code is a cudaError_t)" : "unknown code";
+    }
+}

@@ -26,7 +26,7 @@ from concurrent.futures import ThreadPoolExecutor
 from typing import Dict, Iterable, List, Optional
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_HEADERS = ("common.cuh", "tc_common.cuh")
+_HEADERS = ("common.cuh", "tc_common.cuh", "attention_noalloc.h")
 _FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
