@@ -30,48 +30,75 @@
 namespace zlm {
 
 // ------------------------------------------------------- rope + cache write
-// grid (T, n_heads + 2*n_kv_heads); a thread per rotated pair, then per copied element
+// One block per token.  The cosines and sines of the token's position are formed once in shared
+// memory (float32 angles), then the threads walk the heads: q and k heads are rotated in place,
+// k (rotated) and v heads are copied to the token's row of the cache pages.
 // qkv row layout: [q: n_heads*hd | k: n_kv*hd | v: n_kv*hd]
+constexpr int ROPE_MAX_HALF = 256;
+
 template <typename T>
 __global__ void rope_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
                                   const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                   const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                                   int bt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size,
                                   long page_stride) {
+    __shared__ float cos_s[ROPE_MAX_HALF], sin_s[ROPE_MAX_HALF];
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
-    const int head = blockIdx.y;
     const int pos = positions[t];
-    T* row = qkv + (long)t * row_stride + (long)head * hd;
-    const bool is_q = head < n_heads;
-    const bool is_k = !is_q && head < n_heads + n_kv;
-    T* dst = nullptr;
-    if (!is_q && k_pages != nullptr) {
-        const int kvh = is_k ? head - n_heads : head - n_heads - n_kv;
+    const int half = rot / 2;
+    const bool have_table = inv_freq != nullptr && half > 0;
+    if (have_table) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float theta = (float)pos * inv_freq[i];
+            sincosf(theta, &sin_s[i], &cos_s[i]);
+        }
+    }
+    __syncthreads();
+    T* row0 = qkv + (long)t * row_stride;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (k_pages != nullptr && n_kv > 0) {
         const int b = seq_of_token[t];
         const int page = block_table[(long)b * bt_stride + pos / page_size];
-        T* base = is_k ? k_pages : v_pages;
-        dst = base + (long)page * page_stride + ((long)kvh * page_size + pos % page_size) * hd;
+        const long off = (long)page * page_stride + (long)(pos % page_size) * hd;
+        kdst = k_pages + off;       // head h of the cache row lies h * page_size * hd further
+        vdst = v_pages + off;
     }
-    const int half = rot / 2;
-    const bool rotate = (is_q || is_k) && inv_freq != nullptr;
-    if (rotate) {
-        // one thread per pair: both members are read before either is written
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const int n_rot_heads = n_heads + n_kv;
+    const long kv_head_stride = (long)page_size * hd;
+    // rotated pairs of the q and k heads
+    if (have_table) {
+        for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
+            const int head = idx / half, i = idx - head * half;
+            T* row = row0 + (long)head * hd;
             const float a = to_float(row[i]);
             const float b2 = to_float(row[i + half]);
-            const float theta = (float)pos * inv_freq[i];
-            float s, c;
-            sincosf(theta, &s, &c);
-            const T lo = from_float<T>(a * c - b2 * s);
-            const T hi = from_float<T>(a * s + b2 * c);
+            const float c = cos_s[i], sn = sin_s[i];
+            const T lo = from_float<T>(a * c - b2 * sn);
+            const T hi = from_float<T>(a * sn + b2 * c);
             row[i] = lo;
             row[i + half] = hi;
-            if (dst) { dst[i] = lo; dst[i + half] = hi; }
+            if (kdst && head >= n_heads) {
+                T* d = kdst + (long)(head - n_heads) * kv_head_stride;
+                d[i] = lo;
+                d[i + half] = hi;
+            }
         }
-        if (dst)
-            for (int i = rot + threadIdx.x; i < hd; i += blockDim.x) dst[i] = row[i];
-    } else if (dst) {
-        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst[i] = row[i];
+    }
+    if (kdst) {
+        // what the rotation left alone of the k heads (everything when there is no table), and the v heads
+        const int k_first = have_table ? rot : 0;
+        const int k_rest = hd - k_first;
+        for (int idx = threadIdx.x; idx < n_kv * k_rest; idx += blockDim.x) {
+            const int h = idx / k_rest, i = k_first + idx - h * k_rest;
+            kdst[(long)h * kv_head_stride + i] = row0[(long)(n_heads + h) * hd + i];
+        }
+        for (int idx = threadIdx.x; idx < n_kv * hd; idx += blockDim.x) {
+            const int h = idx / hd, i = idx - h * hd;
+            vdst[(long)h * kv_head_stride + i] = row0[(long)(n_heads + n_kv + h) * hd + i];
+        }
     }
 }
 
@@ -216,21 +243,22 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
     if (T <= 0) return 0;
     if (hd <= 0 || rot < 0 || rot > hd || (rot & 1) || n_heads <= 0 || n_kv < 0 || page_size <= 0)
         return ZLM_ERR_BAD_ARG;
-    int threads = 32;
-    while (threads < hd && threads < 256) threads <<= 1;
-    dim3 grid(T, n_heads + 2 * n_kv);
+    if (rot / 2 > ROPE_MAX_HALF) return ZLM_ERR_UNSUPPORTED;
+    const int work = (n_heads + n_kv) * (hd / 2);
+    const int threads = work >= 2048 ? 256 : (work >= 512 ? 128 : 64);
+    dim3 grid(T);
+    cudaError_t e;
     if (dtype == ZLM_F32)
-        rope_store_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, row_stride, n_heads, n_kv, hd, rot,
-                                                               inv_freq, positions, seq_of_token, block_table,
-                                                               bt_stride, (float*)k_pages, (float*)v_pages,
-                                                               page_size, page_stride);
+        e = launch_pdl(rope_store_kernel<float>, grid, dim3(threads), 0, stream, (float*)qkv, row_stride, n_heads, n_kv,
+                       hd, rot, inv_freq, positions, seq_of_token, block_table, bt_stride, (float*)k_pages,
+                       (float*)v_pages, page_size, page_stride);
     else if (dtype == ZLM_BF16)
-        rope_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-            (__nv_bfloat16*)qkv, row_stride, n_heads, n_kv, hd, rot, inv_freq, positions, seq_of_token, block_table,
-            bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, page_stride);
+        e = launch_pdl(rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)qkv,
+                       row_stride, n_heads, n_kv, hd, rot, inv_freq, positions, seq_of_token, block_table, bt_stride,
+                       (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, page_stride);
     else
         return ZLM_ERR_UNSUPPORTED;
-    return launch_status();
+    return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 ZLM_EXPORT int zlm_attention_general(const void* q, long q_row_stride, void* out, int dtype, int T, int n_heads,

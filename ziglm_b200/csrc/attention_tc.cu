@@ -245,6 +245,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         fence_mbar_init();
     }
     __syncthreads();
+    pdl_wait();                      // the keys and values of this step are written by the kernel before
+    pdl_launch_dependents();
 
     const int gid = lane >> 2, tid4 = lane & 3;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -323,6 +325,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, int n_splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long row = blockIdx.x;                    // t * n_heads + h
     float big = -INFINITY;
     for (int s = 0; s < n_splits; ++s) big = fmaxf(big, part_ml[(row * n_splits + s) * 2]);
@@ -379,6 +383,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         fence_mbar_init();
     }
     __syncthreads();
+    pdl_wait();
+    pdl_launch_dependents();
 
     if (warp == ATC_CONSUMERS) {
         if (lane == 0)
@@ -551,16 +557,22 @@ ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out,
         static bool done = false;
         rc = set_smem(attn_decode_kernel<128>, CFG128::SMEM, &done);
         if (rc) return rc;
-        attn_decode_kernel<128><<<grid, ATC_THREADS, CFG128::SMEM, stream>>>(mk, mv, a, positions, seq_of_token,
-                                                                                 part_o, part_ml);
-        attn_merge_kernel<128><<<T * n_heads, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits);
+        cudaError_t e = launch_pdl(attn_decode_kernel<128>, grid, dim3(ATC_THREADS), CFG128::SMEM, stream, mk, mv, a,
+                                   positions, seq_of_token, part_o, part_ml);
+        if (e == cudaSuccess)
+            e = launch_pdl(attn_merge_kernel<128>, dim3(T * n_heads), dim3(128), 0, stream, (const float*)part_o,
+                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits);
+        if (e != cudaSuccess) return (int)e;
     } else {
         static bool done = false;
         rc = set_smem(attn_decode_kernel<64>, CFG64::SMEM, &done);
         if (rc) return rc;
-        attn_decode_kernel<64><<<grid, ATC_THREADS, CFG64::SMEM, stream>>>(mk, mv, a, positions, seq_of_token,
-                                                                               part_o, part_ml);
-        attn_merge_kernel<64><<<T * n_heads, 64, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits);
+        cudaError_t e = launch_pdl(attn_decode_kernel<64>, grid, dim3(ATC_THREADS), CFG64::SMEM, stream, mk, mv, a,
+                                   positions, seq_of_token, part_o, part_ml);
+        if (e == cudaSuccess)
+            e = launch_pdl(attn_merge_kernel<64>, dim3(T * n_heads), dim3(64), 0, stream, (const float*)part_o,
+                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits);
+        if (e != cudaSuccess) return (int)e;
     }
     return launch_status();
 }
@@ -584,14 +596,16 @@ ZLM_EXPORT int zlm_attention_prefill(const void* q, long q_row_stride, void* out
         static bool done = false;
         rc = set_smem(attn_prefill_kernel<128>, CFG128::SMEM, &done);
         if (rc) return rc;
-        attn_prefill_kernel<128><<<grid, ATC_THREADS, CFG128::SMEM, stream>>>(mk, mv, a, cu_seqlens, past_lens,
-                                                                                  (__nv_bfloat16*)out);
+        cudaError_t e = launch_pdl(attn_prefill_kernel<128>, grid, dim3(ATC_THREADS), CFG128::SMEM, stream, mk, mv, a,
+                                   cu_seqlens, past_lens, (__nv_bfloat16*)out);
+        if (e != cudaSuccess) return (int)e;
     } else {
         static bool done = false;
         rc = set_smem(attn_prefill_kernel<64>, CFG64::SMEM, &done);
         if (rc) return rc;
-        attn_prefill_kernel<64><<<grid, ATC_THREADS, CFG64::SMEM, stream>>>(mk, mv, a, cu_seqlens, past_lens,
-                                                                                (__nv_bfloat16*)out);
+        cudaError_t e = launch_pdl(attn_prefill_kernel<64>, grid, dim3(ATC_THREADS), CFG64::SMEM, stream, mk, mv, a,
+                                   cu_seqlens, past_lens, (__nv_bfloat16*)out);
+        if (e != cudaSuccess) return (int)e;
     }
     return launch_status();
 }

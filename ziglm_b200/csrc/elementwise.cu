@@ -17,6 +17,8 @@ namespace zlm {
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int d, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const long row = (long)tokens[t] * d;
     float* o = out + (long)t * d;
@@ -26,22 +28,88 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
 // ------------------------------------------------------------------ RMSNorm
 // One block per output row.  rows == nullptr: row r of the input; otherwise row
 // rows[r] (this is how the final norm runs on the wanted positions only).
-template <typename TW, typename TO>
+template <typename TO> __device__ __forceinline__ void store4(TO* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+template <typename TW> __device__ __forceinline__ void load4(const TW* p, float (&w)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&w)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&w)[4]) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    w[0] = a.x; w[1] = a.y; w[2] = b.x; w[3] = b.y;
+}
+
+// VEC: the row length is a multiple of 4 and every pointer is 16-byte aligned, so a thread moves four
+// elements at a time and keeps up to MAXV groups of its row in registers between the two passes.
+template <typename TW, typename TO, bool VEC>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int d, float eps, float weight_offset) {
     __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const float* xr = x + (long)(rows ? rows[r] : r) * d;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = xr[i];
-        ss = fmaf(v, v, ss);
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
     TO* o = out + (long)r * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x)
-        o[i] = from_float<TO>((xr[i] * inv) * (to_float(w[i]) + weight_offset));
+    if (VEC) {
+        constexpr int MAXV = 8;
+        float4 keep[MAXV];
+        const int n4 = d >> 2;
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAXV; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n4) {
+                keep[k] = reinterpret_cast<const float4*>(xr)[i];
+                ss = fmaf(keep[k].x, keep[k].x, ss); ss = fmaf(keep[k].y, keep[k].y, ss);
+                ss = fmaf(keep[k].z, keep[k].z, ss); ss = fmaf(keep[k].w, keep[k].w, ss);
+            }
+        }
+        for (int i = threadIdx.x + MAXV * blockDim.x; i < n4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int k = 0; k < MAXV; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < n4) {
+                float ww[4];
+                load4<TW>(w + 4 * i, ww);
+                store4<TO>(o + 4 * i, (keep[k].x * inv) * (ww[0] + weight_offset), (keep[k].y * inv) * (ww[1] + weight_offset),
+                           (keep[k].z * inv) * (ww[2] + weight_offset), (keep[k].w * inv) * (ww[3] + weight_offset));
+            }
+        }
+        for (int i = threadIdx.x + MAXV * blockDim.x; i < n4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            float ww[4];
+            load4<TW>(w + 4 * i, ww);
+            store4<TO>(o + 4 * i, (v.x * inv) * (ww[0] + weight_offset), (v.y * inv) * (ww[1] + weight_offset),
+                       (v.z * inv) * (ww[2] + weight_offset), (v.w * inv) * (ww[3] + weight_offset));
+        }
+    } else {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = xr[i];
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int i = threadIdx.x; i < d; i += blockDim.x)
+            o[i] = from_float<TO>((xr[i] * inv) * (to_float(w[i]) + weight_offset));
+    }
 }
 
 // --------------------------------------------------------- gated activation
@@ -50,6 +118,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, long total, int I, int kind,
                                  int interleaved) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const long t = idx / I;
@@ -93,29 +163,36 @@ ZLM_EXPORT int zlm_embed(const void* table, int table_dtype, const int* tokens, 
     if (T <= 0) return 0;
     if (d <= 0) return ZLM_ERR_BAD_ARG;
     const int threads = d >= 1024 ? 256 : 128;
+    cudaError_t e;
     if (table_dtype == ZLM_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, d, scale);
+        e = launch_pdl(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, tokens, out, d, scale);
     else if (table_dtype == ZLM_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, d, scale);
+        e = launch_pdl(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table,
+                       tokens, out, d, scale);
     else
         return ZLM_ERR_UNSUPPORTED;
-    return launch_status();
+    return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 ZLM_EXPORT int zlm_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype, const int* rows,
                            int n_rows, int d, float eps, float weight_offset, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (d <= 0) return ZLM_ERR_BAD_ARG;
-    const int threads = norm_threads(d);
-#define ZLM_NORM(TW, TO)                                                                                      \
-    rmsnorm_kernel<TW, TO><<<n_rows, threads, 0, stream>>>(x, (const TW*)w, (TO*)out, rows, d, eps, weight_offset)
+    const bool vec = d % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const int threads = vec ? (d >= 2048 ? 256 : (d >= 512 ? 128 : 64)) : norm_threads(d);
+    cudaError_t e;
+#define ZLM_NORM(TW, TO)                                                                                       \
+    e = vec ? launch_pdl(rmsnorm_kernel<TW, TO, true>, dim3(n_rows), dim3(threads), 0, stream, x, (const TW*)w,  \
+                         (TO*)out, rows, d, eps, weight_offset)                                                \
+            : launch_pdl(rmsnorm_kernel<TW, TO, false>, dim3(n_rows), dim3(threads), 0, stream, x, (const TW*)w, \
+                         (TO*)out, rows, d, eps, weight_offset)
     if (w_dtype == ZLM_F32 && out_dtype == ZLM_F32) ZLM_NORM(float, float);
     else if (w_dtype == ZLM_F32 && out_dtype == ZLM_BF16) ZLM_NORM(float, __nv_bfloat16);
     else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_F32) ZLM_NORM(__nv_bfloat16, float);
     else if (w_dtype == ZLM_BF16 && out_dtype == ZLM_BF16) ZLM_NORM(__nv_bfloat16, __nv_bfloat16);
     else return ZLM_ERR_UNSUPPORTED;
 #undef ZLM_NORM
-    return launch_status();
+    return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 ZLM_EXPORT int zlm_gated_act(const void* gu, void* out, int dtype, int T, int I, int kind, int interleaved,
@@ -125,16 +202,16 @@ ZLM_EXPORT int zlm_gated_act(const void* gu, void* out, int dtype, int T, int I,
     const long total = (long)T * I;
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    cudaError_t e;
     if (dtype == ZLM_F32)
-        gated_act_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, I, kind,
-                                                                 interleaved);
+        e = launch_pdl(gated_act_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out,
+                       total, I, kind, interleaved);
     else if (dtype == ZLM_BF16)
-        gated_act_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu,
-                                                                         (__nv_bfloat16*)out, total, I, kind,
-                                                                         interleaved);
+        e = launch_pdl(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream,
+                       (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, I, kind, interleaved);
     else
         return ZLM_ERR_UNSUPPORTED;
-    return launch_status();
+    return e == cudaSuccess ? launch_status() : (int)e;
 }
 
 ZLM_EXPORT int zlm_add(float* y, const float* x, long n, cudaStream_t stream) {

@@ -9,7 +9,7 @@
 //   warp 1   issues tcgen05.mma (M=128, N=BN, K=16, bf16 -> float) from the stages
 //            into an accumulator in tensor memory, and frees a stage with
 //            tcgen05.commit when its instructions have read it;
-//   warps 2-5 read the accumulator with tcgen05.ld, add the bias, stage the tile in
+//   warps 2-9 read the accumulator with tcgen05.ld, add the bias, stage the tile in
 //            shared memory and hand it to one TMA store (float or bf16 output) or one
 //            TMA reduce-add (sum into a float output: the residual stream).  In the
 //            gated mode the weight rows alternate gate and up rows and the epilogue
@@ -35,10 +35,11 @@ using namespace tc;
 constexpr int TC_BM = 128;          // weight rows per tile (UMMA M)
 constexpr int TC_BK = 64;           // K elements per stage: one 128-byte swizzle row
 constexpr int TC_UMMA_K = 16;
-constexpr int TC_THREADS = 192;
+constexpr int TC_EPI_WARPS = 8;                 // two per TMEM lane quarter: they take alternate 16-token chunks
+constexpr int TC_THREADS = (2 + TC_EPI_WARPS) * 32;
 constexpr int A_BYTES = TC_BM * TC_BK * 2;
 
-enum OutMode { OUT_F32 = 0, OUT_F32_ACC = 1, OUT_BF16 = 2, OUT_BF16_GLU = 3 };
+enum OutMode { OUT_F32 = 0, OUT_F32_ACC = 1, OUT_BF16 = 2, OUT_BF16_GLU = 3, OUT_BF16_GEGLU = 4 };
 
 struct TcArgs {
     const void* bias;
@@ -65,9 +66,23 @@ template <int BN> struct TcCfg {
     static constexpr int ACC_COLS = BN;                            // columns of one accumulator
     static constexpr int COLS = 2 * BN < 32 ? 32 : 2 * BN;         // two accumulators: a power of two >= 32
     static constexpr int SUB = sub_rows(BN);                       // tokens staged per TMA store
-    static constexpr int STAGING = SUB * TC_BM * 4;
+    static constexpr int NBUF = BN >= 128 ? 2 : 1;                 // staging buffers: a store drains while the next fills
+    static constexpr int SUB_BYTES = SUB * TC_BM * 4;
+    static constexpr int STAGING = NBUF * SUB_BYTES;
     static constexpr int SMEM = 1024 + STAGES * (A_BYTES + B_BYTES) + STAGING + 256;
 };
+
+// silu(g) = g / (1 + exp(-g)), or the tanh form of gelu; fast exponentials (the result is rounded to bf16)
+template <bool GELU>
+__device__ __forceinline__ float gated_activation(float g) {
+    if (GELU) {
+        // tanh(z) = 1 - 2 / (exp(2z) + 1)
+        const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        const float th = 1.0f - __fdividef(2.0f, __expf(2.0f * z) + 1.0f);
+        return 0.5f * g * (1.0f + th);
+    }
+    return __fdividef(g, 1.0f + __expf(-g));
+}
 
 __device__ __forceinline__ void grid_dependents_may_launch() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -84,7 +99,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                const __grid_constant__ CUtensorMap tmap_y, TcArgs a) {
     using C = TcCfg<BN>;
     constexpr int STAGES = C::STAGES;
-    constexpr bool GLU = MODE == OUT_BF16_GLU;
+    constexpr bool GLU = MODE == OUT_BF16_GLU || MODE == OUT_BF16_GEGLU;
     constexpr int OUT_COLS = GLU ? TC_BM / 2 : TC_BM;              // output features of a tile
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -120,7 +135,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full0 + 8 * b, 1);
-            mbar_init(acc_empty0 + 8 * b, 4);
+            mbar_init(acc_empty0 + 8 * b, TC_EPI_WARPS);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -216,11 +231,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         // ---------------------------------------------------------------- epilogue
         grid_dependency_wait();                     // the output may still be read by the kernel before this one
         const int q = warp & 3;                     // TMEM lane quarter this warp may read
+        const int egroup = (warp - 2) >> 2;         // which of the two warps of that quarter
         const int f_local = q * 32 + lane;
         const bool writer = !GLU || (lane & 1) == 0;
         const int col = GLU ? f_local >> 1 : f_local;
-        float* stage_f = reinterpret_cast<float*>(smem + (stage_out - base));
-        __nv_bfloat16* stage_h = reinterpret_cast<__nv_bfloat16*>(stage_f);
+        uint8_t* stage_base = smem + (stage_out - base);
+        int sub_idx = 0;                            // sub-tiles stored so far by this block
         const uint32_t part_addr = smem_u32(partial);
         int local = 0;
         if (a.splits > 1) {
@@ -230,13 +246,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             const int tile = blockIdx.x;
             const int row0 = (tile / tok_tiles) * TC_BM, tok0 = (tile % tok_tiles) * BN;
             if (n_kb > 0) mbar_wait(acc_full0, 0, abort_flag, a.err, ERR_WAIT_ACCUM);
-            asm volatile("bar.sync 2, 128;" ::: "memory");
+            asm volatile("bar.sync 2, 256;" ::: "memory");
             const bool good = *abort_flag == 0;
             tc_fence_after_sync();
             const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
             if (good) {
 #pragma unroll 1
-                for (int c = 0; c < BN / 16; ++c) {
+                for (int c = egroup; c < BN / 16; c += 2) {
                     uint32_t v[16];
                     tmem_ld16(t_lane + c * 16, v);
                     tmem_ld_wait();
@@ -258,7 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             uint32_t remote[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r) remote[r] = r < a.splits ? map_to_rank(part_addr, (uint32_t)r) : 0u;
-            for (int cc = c_lo; cc < c_hi && good; ++cc) {
+            for (int cc = c_lo + egroup; cc < c_hi && good; cc += 2) {
                 const int tok = tok0 + cc;
                 if (tok >= a.T) break;
                 float part[8];
@@ -272,12 +288,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 if (GLU) {
                     const float up = __shfl_down_sync(0xffffffffu, val, 1);
                     const float g = val;
-                    if (a.glu_kind == 0) val = __fdividef(g, 1.0f + __expf(-g));
-                    else val = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-                    val *= up;
+                    val = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
                 }
                 if (writer && out_f < out_n) {
-                    if (MODE == OUT_BF16 || MODE == OUT_BF16_GLU)
+                    if (MODE == OUT_BF16 || GLU)
                         reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
                     else if (MODE == OUT_F32_ACC)       // one adder per element: the order is fixed
                         atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
@@ -290,7 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             const int row0 = (tile / tok_tiles) * TC_BM, tok0 = (tile % tok_tiles) * BN;
             const int ab = local & 1;
             if (n_kb > 0) mbar_wait(acc_full0 + 8 * ab, (local >> 1) & 1, abort_flag, a.err, ERR_WAIT_ACCUM);
-            asm volatile("bar.sync 2, 128;" ::: "memory");     // the four warps go on together or not at all
+            asm volatile("bar.sync 2, 256;" ::: "memory");     // the four warps go on together or not at all
             if (*abort_flag) break;
             tc_fence_after_sync();
             const uint32_t t_lane = tmem_base + ab * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
@@ -306,24 +320,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             for (int c = 0; c < BN / 16; ++c) {
                 if (tok0 + c * 16 >= a.T) break;            // whole chunk beyond the last token (uniform per block)
                 const int sub_row = (c * 16) % C::SUB;       // row of this chunk inside the staged sub-tile
-                if (a.tma_store && sub_row == 0 && (c > 0 || local > 0)) {
-                    // the previous sub-tile must have left shared memory before it is overwritten
-                    if (warp == 2 && lane == 0) tma_store_wait_read();
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int buf = sub_idx % C::NBUF;
+                float* stage_f = reinterpret_cast<float*>(stage_base + buf * C::SUB_BYTES);
+                __nv_bfloat16* stage_h = reinterpret_cast<__nv_bfloat16*>(stage_f);
+                if (a.tma_store && sub_row == 0 && sub_idx >= C::NBUF) {
+                    // the store that last used this buffer must have read it before it is overwritten
+                    if (warp == 2 && lane == 0) tma_store_wait_read_keep<C::NBUF - 1>();
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
                 }
                 uint32_t v[16];
-                tmem_ld16(t_lane + c * 16, v);
-                tmem_ld_wait();
+                const bool mine = (c & 1) == egroup;           // the other warp of this quarter takes the other chunks
+                if (mine) {
+                    tmem_ld16(t_lane + c * 16, v);
+                    tmem_ld_wait();
+                }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
+                    if (!mine) break;
                     float val = __uint_as_float(v[j]) + bias_v;
                     if (GLU) {
                         // even lanes hold a gate row, the next lane the matching up row
                         const float up = __shfl_down_sync(0xffffffffu, val, 1);
                         const float g = val;
-                        if (a.glu_kind == 0) val = __fdividef(g, 1.0f + __expf(-g));
-                        else val = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
-                        val *= up;
+                        val = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
                     }
                     if (a.tma_store) {
                         if (writer) {
@@ -333,7 +352,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     } else {
                         const int tok = tok0 + c * 16 + j;
                         if (writer && tok < a.T && out_f < out_n) {
-                            if (MODE == OUT_BF16 || MODE == OUT_BF16_GLU)
+                            if (MODE == OUT_BF16 || GLU)
                                 reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
                             else if (MODE == OUT_F32_ACC)   // one adder per element: the order is fixed
                                 atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
@@ -345,15 +364,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 const bool last_of_sub = sub_row + 16 == C::SUB || c == BN / 16 - 1 || tok0 + (c + 1) * 16 >= a.T;
                 if (a.tma_store && last_of_sub) {
                     fence_proxy_async();                    // the staged rows become visible to the TMA engine
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
                     if (warp == 2 && lane == 0) {
                         const int x = GLU ? row0 >> 1 : row0;
                         const int y = tok0 + c * 16 - sub_row;
-                        if (MODE == OUT_F32_ACC) tma_reduce_add_2d(&tmap_y, stage_out, x, y);
-                        else tma_store_2d(&tmap_y, stage_out, x, y);
+                        if (MODE == OUT_F32_ACC) tma_reduce_add_2d(&tmap_y, stage_out + buf * C::SUB_BYTES, x, y);
+                        else tma_store_2d(&tmap_y, stage_out + buf * C::SUB_BYTES, x, y);
                         tma_store_commit();
                     }
                 }
+                if (a.tma_store && last_of_sub) ++sub_idx;
             }
             // this accumulator may be overwritten by the tile after next
             tc_fence_before_sync();
@@ -504,6 +524,7 @@ static int pick_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, con
         case OUT_F32: return launch_tc<BN, OUT_F32>(mw, mx, my, a, s);
         case OUT_F32_ACC: return launch_tc<BN, OUT_F32_ACC>(mw, mx, my, a, s);
         case OUT_BF16_GLU: return launch_tc<BN, OUT_BF16_GLU>(mw, mx, my, a, s);
+        case OUT_BF16_GEGLU: return launch_tc<BN, OUT_BF16_GEGLU>(mw, mx, my, a, s);
         default: return launch_tc<BN, OUT_BF16>(mw, mx, my, a, s);
     }
 }
@@ -564,7 +585,9 @@ ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int b
     if (rc) return rc;
     rc = cached_map(&mx, X, T, K, ldx, bn);
     if (rc) return rc;
-    const int mode = glu ? OUT_BF16_GLU : (y_dtype == ZLM_BF16 ? OUT_BF16 : (accumulate ? OUT_F32_ACC : OUT_F32));
+    const int mode = glu == 1 ? OUT_BF16_GLU
+                     : glu == 2 ? OUT_BF16_GEGLU
+                                : (y_dtype == ZLM_BF16 ? OUT_BF16 : (accumulate ? OUT_F32_ACC : OUT_F32));
     // the output goes through TMA when its rows start on 16-byte boundaries; else the threads store directly
     const int es = y_dtype == ZLM_BF16 ? 2 : 4;
     static const bool no_tma_store = getenv("ZLM_NO_TMA_STORE") != nullptr;

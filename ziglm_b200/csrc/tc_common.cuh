@@ -93,6 +93,12 @@ __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+// Wait until all but the N most recent committed stores have read their shared memory.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read_keep() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
 // Wait until every committed store has read its shared memory (the issuing thread calls this).
 __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
