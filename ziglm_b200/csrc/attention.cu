@@ -66,12 +66,15 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, long row_stride, int n_he
         kdst = k_pages + off;       // head h of the cache row lies h * page_size * hd further
         vdst = v_pages + off;
     }
-    const int n_rot_heads = n_heads + n_kv;
     const long kv_head_stride = (long)page_size * hd;
-    // rotated pairs of the q and k heads
-    if (have_table) {
-        for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
-            const int head = idx / half, i = idx - head * half;
+    // this block's share of the heads, counted over q heads, k heads, v heads in that order
+    const int total_heads = n_heads + 2 * n_kv;
+    const int per = (total_heads + gridDim.y - 1) / gridDim.y;
+    const int h_lo = blockIdx.y * per, h_hi = min(total_heads, h_lo + per);
+    const int rot_hi = min(h_hi, n_heads + n_kv);            // heads below this one are rotated
+    if (have_table && rot_hi > h_lo) {
+        for (int idx = threadIdx.x; idx < (rot_hi - h_lo) * half; idx += blockDim.x) {
+            const int head = h_lo + idx / half, i = idx % half;
             T* row = row0 + (long)head * hd;
             const float a = to_float(row[i]);
             const float b2 = to_float(row[i + half]);
@@ -91,12 +94,14 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, long row_stride, int n_he
         // what the rotation left alone of the k heads (everything when there is no table), and the v heads
         const int k_first = have_table ? rot : 0;
         const int k_rest = hd - k_first;
-        for (int idx = threadIdx.x; idx < n_kv * k_rest; idx += blockDim.x) {
-            const int h = idx / k_rest, i = k_first + idx - h * k_rest;
+        const int k_lo = max(h_lo, n_heads), k_hi = rot_hi;
+        for (int idx = threadIdx.x; idx < (k_hi - k_lo) * k_rest; idx += blockDim.x) {
+            const int h = k_lo - n_heads + idx / k_rest, i = k_first + idx % k_rest;
             kdst[(long)h * kv_head_stride + i] = row0[(long)(n_heads + h) * hd + i];
         }
-        for (int idx = threadIdx.x; idx < n_kv * hd; idx += blockDim.x) {
-            const int h = idx / hd, i = idx - h * hd;
+        const int v_lo = max(h_lo, n_heads + n_kv);
+        for (int idx = threadIdx.x; idx < (h_hi - v_lo) * hd; idx += blockDim.x) {
+            const int h = v_lo - n_heads - n_kv + idx / hd, i = idx % hd;
             vdst[(long)h * kv_head_stride + i] = row0[(long)(n_heads + n_kv + h) * hd + i];
         }
     }
@@ -244,9 +249,16 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
     if (hd <= 0 || rot < 0 || rot > hd || (rot & 1) || n_heads <= 0 || n_kv < 0 || page_size <= 0)
         return ZLM_ERR_BAD_ARG;
     if (rot / 2 > ROPE_MAX_HALF) return ZLM_ERR_UNSUPPORTED;
-    const int work = (n_heads + n_kv) * (hd / 2);
+    // few tokens (a decode step): the heads of a token are shared out over several blocks
+    const int total_heads = n_heads + 2 * n_kv;
+    int parts = (296 + T - 1) / T;
+    if (parts > total_heads) parts = total_heads;
+    if (parts < 1) parts = 1;
+    const int per = (total_heads + parts - 1) / parts;
+    parts = (total_heads + per - 1) / per;
+    const int work = per * (hd / 2);
     const int threads = work >= 2048 ? 256 : (work >= 512 ? 128 : 64);
-    dim3 grid(T);
+    dim3 grid(T, parts);
     cudaError_t e;
     if (dtype == ZLM_F32)
         e = launch_pdl(rope_store_kernel<float>, grid, dim3(threads), 0, stream, (float*)qkv, row_stride, n_heads, n_kv,

@@ -54,6 +54,13 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x on the special function unit (flushes denormals; exact enough before rounding to bf16)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -93,7 +100,8 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[HD / 16][4], const _
 //   key0        first key (row of the tile) this warp reads
 //   gkey0       position in the sequence of that key
 //   lim_lo/hi   last visible position of rows gid / gid+8;  start_lo/hi first visible one
-template <int HD, int NT>
+//   FULL        every key of the step is visible to every row: no masks are evaluated
+template <int HD, int NT, bool FULL>
 __device__ __forceinline__ void page_step(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, uint32_t v_tile, int key0,
                                           int gkey0, int lim_lo, int lim_hi, int start_lo, int start_hi,
                                           float scale_log2, float (&m)[2], float (&l)[2], float (&o)[HD / 8][4],
@@ -119,10 +127,14 @@ __device__ __forceinline__ void page_step(const uint32_t (&qf)[HD / 16][4], uint
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int key = gkey0 + nt * 8 + 2 * tid4 + (i & 1);
             const bool hi = i >= 2;
-            const bool vis = key <= (hi ? lim_hi : lim_lo) && key >= (hi ? start_hi : start_lo);
-            s[nt][i] = vis ? s[nt][i] * scale_log2 : -INFINITY;
+            if (FULL) {
+                s[nt][i] *= scale_log2;
+            } else {
+                const int key = gkey0 + nt * 8 + 2 * tid4 + (i & 1);
+                const bool vis = key <= (hi ? lim_hi : lim_lo) && key >= (hi ? start_hi : start_lo);
+                s[nt][i] = vis ? s[nt][i] * scale_log2 : -INFINITY;
+            }
             mx[hi] = fmaxf(mx[hi], s[nt][i]);
         }
     }
@@ -133,7 +145,7 @@ __device__ __forceinline__ void page_step(const uint32_t (&qf)[HD / 16][4], uint
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
         const float m_new = fmaxf(m[h], mx[h]);
         use[h] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen no key yet
-        corr[h] = exp2f(m[h] - use[h]);                      // exp2(-inf) = 0 the first time
+        corr[h] = fast_exp2(m[h] - use[h]);                  // 2^(-inf) = 0 the first time
         m[h] = m_new;
         l[h] *= corr[h];
     }
@@ -141,14 +153,17 @@ __device__ __forceinline__ void page_step(const uint32_t (&qf)[HD / 16][4], uint
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            s[nt][i] = exp2f(s[nt][i] - use[i >> 1]);
+            s[nt][i] = fast_exp2(s[nt][i] - use[i >> 1]);
             l[i >> 1] += s[nt][i];
         }
     }
+    // the running maxima settle after a few pages; the accumulators are rescaled only when one moved
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) {
-        o[n][0] *= corr[0]; o[n][1] *= corr[0];
-        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        for (int n = 0; n < HD / 8; ++n) {
+            o[n][0] *= corr[0]; o[n][1] *= corr[0];
+            o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        }
     }
 #pragma unroll
     for (int kp = 0; kp < NT / 2; ++kp) {
@@ -271,8 +286,12 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         for (int p = page_lo; p < page_hi; ++p, ++it) {
             const int s = it % C::STAGES;
             if (!mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL)) break;
-            page_step<HD, 2>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16, pos, pos,
-                             start, start, a.scale_log2, m, l, o, lane);
+            if (p * PAGE >= start && p * PAGE + PAGE - 1 <= pos)
+                page_step<HD, 2, true>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
+                                       pos, pos, start, start, a.scale_log2, m, l, o, lane);
+            else
+                page_step<HD, 2, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
+                                        pos, pos, start, start, a.scale_log2, m, l, o, lane);
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
@@ -405,6 +424,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     // the warp's rows span positions [w_first, w_last]: pages wholly outside need no work
     const int w_first = past + q0 + warp * 16, w_last = min(pos_last, w_first + 15);
     const int w_start = (a.window > 0 && w_first - a.window + 1 > 0) ? w_first - a.window + 1 : 0;
+    const int w_last_start = (a.window > 0 && w_last - a.window + 1 > 0) ? w_last - a.window + 1 : 0;
+    const bool w_rows_all = w_first + 15 <= pos_last;        // all 16 rows of the warp are real tokens
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[HD / 8][4];
@@ -418,9 +439,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         const int s = it % C::STAGES;
         if (!mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL)) break;
         const bool needed = w_first <= pos_last && p * PAGE <= w_last && p * PAGE + PAGE - 1 >= w_start;
-        if (needed)
-            page_step<HD, 8>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, 0, p * PAGE, lim_lo, lim_hi, st_lo, st_hi,
-                             a.scale_log2, m, l, o, lane);
+        if (needed) {
+            // a page every row of the warp sees whole needs no masks (rows beyond the sequence never store)
+            const bool full = p * PAGE + PAGE - 1 <= w_first && p * PAGE >= w_last_start && w_rows_all;
+            if (full)
+                page_step<HD, 8, true>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, 0, p * PAGE, lim_lo, lim_hi,
+                                       st_lo, st_hi, a.scale_log2, m, l, o, lane);
+            else
+                page_step<HD, 8, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, 0, p * PAGE, lim_lo, lim_hi,
+                                        st_lo, st_hi, a.scale_log2, m, l, o, lane);
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8 * s);
     }
@@ -503,6 +531,9 @@ template <typename Kern>
 static int set_smem(Kern kern, int bytes, bool* done) {
     if (*done) return 0;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    // ask for the largest shared-memory carve-out, so that several blocks fit an SM
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
     *done = true;
     return 0;

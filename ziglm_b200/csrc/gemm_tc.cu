@@ -490,6 +490,10 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const CUtenso
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              C::SMEM);
         if (e != cudaSuccess) return (int)e;
+        // ask for the largest shared-memory carve-out, so that two blocks of the narrow tiles fit an SM
+        e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
