@@ -282,6 +282,58 @@ def run_ours(args):
     return 0
 
 
+def run_case(args):
+    """A single phase on a (possibly shallower) model, for profilers: the prompt of 2,048 tokens, or decode steps."""
+    import torch
+    from ziglm_b200 import Engine, EngineOptions, config_from_dict, kernels
+    torch.cuda.set_device(0)
+    cfg = dict(LLAMA_8B)
+    cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
+    batch, context = args.batch, args.context
+    max_seq = context + 64
+    eng = Engine.from_config(config_from_dict(cfg), EngineOptions(
+        dtype="bfloat16", max_batch=batch, max_seq_len=max_seq, max_tokens=batch * (-(-max_seq // 64) * 64), seed=1234))
+    gen = torch.Generator().manual_seed(7)
+    ids = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
+    times = []
+    if args.case == "prefill":
+        prompt = ids(PREFILL_TOKENS)
+        for k in range(args.warmup + args.steps):
+            slot = eng.alloc_slot()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            eng.step([(slot, prompt)])
+            e.record()
+            torch.cuda.synchronize()
+            if k >= args.warmup:
+                times.append(s.elapsed_time(e))
+            eng.free_slot(slot)
+        tokens = PREFILL_TOKENS
+    else:
+        slots = [eng.alloc_slot() for _ in range(batch)]
+        # the cache is given its length without being computed: a decode step's time does not depend on its content
+        grow = {s: context - args.warmup - args.steps - 1 for s in slots}
+        eng.cache.slots.reserve(grow)
+        eng.cache.slots.advance(grow)
+        for k in range(args.warmup + args.steps):
+            toks = ids(batch)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s.record()
+            eng.step([(sl, [t]) for sl, t in zip(slots, toks)])
+            e.record()
+            torch.cuda.synchronize()
+            if k >= args.warmup:
+                times.append(s.elapsed_time(e))
+        tokens = batch
+    ms = sorted(times)[len(times) // 2]
+    print(json.dumps({"case": args.case, "layers": cfg["num_hidden_layers"], "batch": batch, "context": context,
+                      "ms": round(ms, 4), "tok_s": round(tokens / ms * 1000.0, 1),
+                      "wait_errors": [kernels.gemm_tc_status(), kernels.attention_tc_status()]}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -290,6 +342,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--case", default="full", choices=["full", "prefill", "decode"],
+                    help="full: the whole measurement; prefill / decode: that phase alone (for profilers)")
+    ap.add_argument("--batch", type=int, default=8, help="--case decode: sequences in the batch")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="--case decode: tokens each sequence holds")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -299,6 +355,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this library has no multi-GPU path (asked for --gpus {args.gpus})")
         return 2
+    if args.case != "full":
+        return run_case(args)
     return run_ours(args)
 
 

@@ -363,7 +363,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 
 // ------------------------------------------------------------------ prefill
 template <int HD>
-__global__ void __launch_bounds__(ATC_THREADS)
+__global__ void __launch_bounds__(ATC_THREADS, 2)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, AtcCommon a,
                     const int* __restrict__ cu_seqlens, const int* __restrict__ past_lens,
                     __nv_bfloat16* __restrict__ out) {

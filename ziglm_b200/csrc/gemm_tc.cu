@@ -60,8 +60,9 @@ struct TcArgs {
 __host__ __device__ constexpr int sub_rows(int bn) { return (bn == 16 || bn == 64) ? 16 : 32; }
 
 template <int BN> struct TcCfg {
-    // two blocks share an SM up to BN = 64 (each may use about 113 KB of shared memory)
-    static constexpr int STAGES = BN <= 16 ? 5 : (BN == 128 ? 5 : 4);
+    // Narrow tiles (decode steps) keep few stages, so that three or four blocks fit an SM: the blocks of
+    // the next product become resident while this one drains and request their weight tiles early.
+    static constexpr int STAGES = BN <= 32 ? 3 : (BN == 128 ? 5 : 4);
     static constexpr int B_BYTES = BN * TC_BK * 2;
     static constexpr int ACC_COLS = BN;                            // columns of one accumulator
     static constexpr int COLS = 2 * BN < 32 ? 32 : 2 * BN;         // two accumulators: a power of two >= 32
