@@ -120,11 +120,14 @@ def test_attention_decode(K, hd, nh, nkv, window, n_splits):
     assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("kernel", ["mma", "fmha"])
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("nh,nkv", [(8, 2), (4, 4), (16, 1)])
 @pytest.mark.parametrize("window", [None, 37, 100])
-def test_attention_prefill(K, hd, nh, nkv, window):
-    lens_past, lens_new = [0, 130, 63, 0, 5], [21, 1, 70, 200, 64]
+def test_attention_prefill(K, kernel, hd, nh, nkv, window):
+    """mma: the mma.sync kernel (64 query rows a block); fmha: the tcgen05 kernel (128 rows, accumulators in
+    tensor memory).  Sequences shorter and longer than a tile, continued ones, one of a single token."""
+    lens_past, lens_new = [0, 130, 63, 0, 5], [21, 1, 70, 300, 128]
     ks, vs, q, positions, seq = dense_attention_case(BF, nh, nkv, hd, lens_past, lens_new, seed=30)
     kp, vp, table = paged(ks, vs, 64, BF, seed=3)
     T = q.shape[0]
@@ -133,17 +136,17 @@ def test_attention_prefill(K, hd, nh, nkv, window):
     cu = [0]
     for n in lens_new:
         cu.append(cu[-1] + n)
-    assert K.attention_prefill(q.reshape(T, nh * hd).to(DEV), out, len(lens_new), max(lens_new), nh, nkv, hd, scale,
-                               window, torch.tensor(cu, dtype=torch.int32, device=DEV),
-                               torch.tensor(lens_past, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV),
-                               vp.to(DEV), 64)
+    fn = K.attention_prefill if kernel == "mma" else K.attention_prefill_fmha
+    assert fn(q.reshape(T, nh * hd).to(DEV), out, len(lens_new), max(lens_new), nh, nkv, hd, scale,
+              window, torch.tensor(cu, dtype=torch.int32, device=DEV),
+              torch.tensor(lens_past, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV), vp.to(DEV), 64)
     torch.cuda.synchronize()
-    assert K.attention_tc_status() == 0
+    assert K.attention_tc_status() == 0 and K.attention_fmha_status() == 0
     want = plain_attention_rows(ks, vs, q, positions, seq, scale, window)
     assert torch.allclose(out.float().cpu().view(T, nh, hd), want, atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+@pytest.mark.parametrize("kernel", ["decode", "prefill", "fmha"])
 @pytest.mark.parametrize("hd", [64, 128])
 def test_tc_attention_finds_one_far_key_and_respects_the_window_edge(K, kernel, hd):
     """One key is made to dominate: far back among hundreds (every page position, split boundary), then just
@@ -168,7 +171,8 @@ def test_tc_attention_finds_one_far_key_and_respects_the_window_edge(K, kernel, 
                                       torch.zeros(1, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV),
                                       vp.to(DEV), 64, ns, po, pm)
         else:
-            assert K.attention_prefill(q.reshape(1, -1).to(DEV), out, 1, 1, nh, nkv, hd, scale, window,
+            fn = K.attention_prefill if kernel == "prefill" else K.attention_prefill_fmha
+            assert fn(q.reshape(1, -1).to(DEV), out, 1, 1, nh, nkv, hd, scale, window,
                                        torch.tensor([0, 1], dtype=torch.int32, device=DEV),
                                        torch.tensor([n - 1], dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV),
                                        vp.to(DEV), 64)

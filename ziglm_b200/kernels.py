@@ -74,6 +74,12 @@ _PROTOTYPES = {
                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "zlm_attention_tc_status": [c_void_p],
     },
+    "attention_fmha": {
+        "zlm_attention_prefill_fmha": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                       c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int,
+                                       c_void_p],
+        "zlm_attention_fmha_status": [c_void_p],
+    },
     "gemm_tc": {
         "zlm_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_long, c_long, c_long, c_int, c_void_p],
@@ -346,6 +352,43 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new
     return True
 
 
+def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, n_kv: int,
+                           head_dim: int, scale: float, window: Optional[int], cu_seqlens: torch.Tensor,
+                           past_lens: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                           v_pages: torch.Tensor, page_size: int) -> bool:
+    """Prompt attention on the tcgen05 tensor cores (tiles of 128 queries, accumulators in tensor memory); same
+    arguments as :func:`attention_prefill`.  False if refused."""
+    _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
+    _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(past_lens, "past_lens", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    if not qkv.is_cuda or qkv.dtype != torch.bfloat16 or qkv.stride(1) != 1:
+        raise KernelError("attention_prefill_fmha: q must be bfloat16 on the device with unit column stride")
+    if out.shape[1] != n_heads * head_dim or qkv.shape[1] < n_heads * head_dim:
+        raise KernelError("attention_prefill_fmha: widths do not match the head counts")
+    if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError("attention_prefill_fmha: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+    if cu_seqlens.numel() < n_seqs + 1 or past_lens.numel() < n_seqs:
+        raise KernelError("attention_prefill_fmha: sequence arrays are too short")
+    status = _fn("attention_fmha", "zlm_attention_prefill_fmha")(
+        qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), n_seqs, max_new, n_heads, n_kv, head_dim, scale,
+        int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, _stream())
+    if status == -2:
+        return False
+    _check(status, "attention_prefill_fmha")
+    return True
+
+
+def attention_fmha_status() -> int:
+    """0, or the code of a bounded wait that ran out inside the tcgen05 attention kernel (21 queries, 22 page,
+    23 scores, 24 probabilities, 25 output, 26 stage never drained, 4 copies still in flight)."""
+    out = ctypes.c_int(0)
+    rc = _fn("attention_fmha", "zlm_attention_fmha_status")(ctypes.byref(out))
+    if rc != 0:
+        raise KernelError(f"attention_fmha_status: CUDA error {rc}")
+    return out.value
+
+
 def attention_tc_status() -> int:
     """0, or the code of a bounded wait that ran out inside a tensor-core attention kernel (11 a page never
     landed, 12 a stage never drained, 4 copies still in flight).  Synchronises the device."""
@@ -375,16 +418,20 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
                                 step.seq_of_token, io.block_table, io.k_pages, io.v_pages, io.page_size, n_splits,
                                 part_o, part_ml):
                 return
-        elif attention_prefill(qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window,
-                               step.cu_seqlens, step.past_lens, io.block_table, io.k_pages, io.v_pages,
-                               io.page_size):
-            return
+        else:
+            # prompts: the tcgen05 kernel (tiles of 128 queries); a handful of tokens: the 64-row mma.sync one
+            args = (qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window, step.cu_seqlens,
+                    step.past_lens, io.block_table, io.k_pages, io.v_pages, io.page_size)
+            if step.max_new >= 16 and attention_prefill_fmha(*args):
+                return
+            if attention_prefill(*args):
+                return
     attention_general(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
                       io.block_table, io.k_pages, io.v_pages, io.page_size)
 
 
 def fast_attention_libraries(dtype: torch.dtype, head_dim: int):
-    return ("attention_tc",) if dtype == torch.bfloat16 and head_dim in (64, 128) else ()
+    return ("attention_tc", "attention_fmha") if dtype == torch.bfloat16 and head_dim in (64, 128) else ()
 
 
 def fast_gemm_libraries():
