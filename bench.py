@@ -330,7 +330,8 @@ def run_case(args):
     ms = sorted(times)[len(times) // 2]
     print(json.dumps({"case": args.case, "layers": cfg["num_hidden_layers"], "batch": batch, "context": context,
                       "ms": round(ms, 4), "tok_s": round(tokens / ms * 1000.0, 1),
-                      "wait_errors": [kernels.gemm_tc_status(), kernels.attention_tc_status()]}))
+                      "wait_errors": [kernels.gemm_tc_status(), kernels.attention_tc_status(),
+                                      kernels.attention_fmha_status()]}))
     return 0
 
 
