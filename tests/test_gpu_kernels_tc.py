@@ -120,6 +120,54 @@ def test_attention_decode(K, hd, nh, nkv, window, n_splits):
     assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
 
 
+def run_decode_flat(K, nh, nkv, hd, lens_past, window, n_blocks, seed=20):
+    lens_new = [1] * len(lens_past)
+    ks, vs, q, positions, seq = dense_attention_case(BF, nh, nkv, hd, lens_past, lens_new, seed=seed)
+    kp, vp, table = paged(ks, vs, 64, BF, seed=2)
+    T = q.shape[0]
+    out = torch.zeros(T, nh * hd, dtype=BF, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    wide = torch.zeros(T, nh * hd + 64, dtype=BF)
+    wide[:, :nh * hd] = q.reshape(T, nh * hd)
+    n_blocks = n_blocks or K.attention_decode_flat_blocks(T, nh, nkv, hd)
+    assert n_blocks > 0
+    # scratch full of NaN: whatever the merge reads must have been written by this call
+    scratch = torch.full((K.attention_decode_flat_scratch(T, nh, nkv, hd, n_blocks),), float("nan"), device=DEV)
+    counters = torch.zeros(T * nkv, dtype=torch.int32, device=DEV)
+    args = (wide.to(DEV), out, nh, nkv, hd, scale, window, torch.tensor(positions, dtype=torch.int32, device=DEV),
+            torch.tensor(seq, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV), vp.to(DEV), 64, n_blocks,
+            counters, scratch)
+    assert K.attention_decode_flat(*args)
+    first = out.clone()
+    assert K.attention_decode_flat(*args)            # the counters are back at zero: a second call is the same
+    torch.cuda.synchronize()
+    assert K.attention_tc_status() == 0
+    assert int(counters.abs().sum()) == 0 and torch.equal(first, out)
+    want = plain_attention_rows(ks, vs, q, positions, seq, scale, window)
+    return out.float().cpu().view(T, nh, hd), want
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (4, 4), (16, 1), (6, 3)])
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("n_blocks", [0, 1, 5, 23])
+def test_attention_decode_flat(K, hd, nh, nkv, window, n_blocks):
+    """The flat kernel: blocks take equal runs of pages that start and end inside sequences.  0 blocks: one
+    resident wave (more blocks than pages here: most have nothing to do); 1: one block walks every sequence;
+    5 and 23: runs that straddle kv heads and sequences of unequal lengths."""
+    got, want = run_decode_flat(K, nh, nkv, hd, [0, 130, 63, 300, 64, 1000, 5], window, n_blocks)
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
+
+
+def test_attention_decode_flat_many_tokens(K):
+    """More tokens than a warp scans at once, lengths of every residue."""
+    lens = [(i * 37) % 200 for i in range(70)]
+    got, want = run_decode_flat(K, 4, 2, 64, lens, None, 0, seed=21)
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
+    got, want = run_decode_flat(K, 4, 2, 128, lens, 50, 7, seed=22)
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("kernel", ["mma", "fmha"])
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("nh,nkv", [(8, 2), (4, 4), (16, 1)])
@@ -146,7 +194,7 @@ def test_attention_prefill(K, kernel, hd, nh, nkv, window):
     assert torch.allclose(out.float().cpu().view(T, nh, hd), want, atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("kernel", ["decode", "prefill", "fmha"])
+@pytest.mark.parametrize("kernel", ["decode", "flat", "prefill", "fmha"])
 @pytest.mark.parametrize("hd", [64, 128])
 def test_tc_attention_finds_one_far_key_and_respects_the_window_edge(K, kernel, hd):
     """One key is made to dominate: far back among hundreds (every page position, split boundary), then just
@@ -170,6 +218,14 @@ def test_tc_attention_finds_one_far_key_and_respects_the_window_edge(K, kernel, 
                                       torch.tensor([n - 1], dtype=torch.int32, device=DEV),
                                       torch.zeros(1, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV),
                                       vp.to(DEV), 64, ns, po, pm)
+        elif kernel == "flat":
+            nb = 3
+            scratch = torch.full((K.attention_decode_flat_scratch(1, nh, nkv, hd, nb),), float("nan"), device=DEV)
+            assert K.attention_decode_flat(q.reshape(1, -1).to(DEV), out, nh, nkv, hd, scale, window,
+                                           torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                                           torch.zeros(1, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV),
+                                           vp.to(DEV), 64, nb, torch.zeros(nkv, dtype=torch.int32, device=DEV),
+                                           scratch)
         else:
             fn = K.attention_prefill if kernel == "prefill" else K.attention_prefill_fmha
             assert fn(q.reshape(1, -1).to(DEV), out, 1, 1, nh, nkv, hd, scale, window,

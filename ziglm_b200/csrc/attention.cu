@@ -43,8 +43,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, long row_stride, int n_he
                                   int bt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size,
                                   long page_stride) {
     __shared__ float cos_s[ROPE_MAX_HALF], sin_s[ROPE_MAX_HALF];
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = rot / 2;

@@ -134,8 +134,8 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
-    pdl_wait();                       // queries, keys and values of this step are written by earlier kernels
     pdl_launch_dependents();
+    pdl_wait();                       // queries, keys and values of this step are written by earlier kernels
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer

@@ -260,8 +260,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         fence_mbar_init();
     }
     __syncthreads();
-    pdl_wait();                      // the keys and values of this step are written by the kernel before
     pdl_launch_dependents();
+    pdl_wait();                      // the keys and values of this step are written by the kernel before
 
     const int gid = lane >> 2, tid4 = lane & 3;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -344,8 +344,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, int n_splits) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const long row = blockIdx.x;                    // t * n_heads + h
     float big = -INFINITY;
     for (int s = 0; s < n_splits; ++s) big = fmaxf(big, part_ml[(row * n_splits + s) * 2]);
@@ -358,6 +358,345 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
             den += part_ml[(row * n_splits + s) * 2 + 1] * wgt;
         }
         out[row * HD + d] = __float2bfloat16_rn(acc / den);
+    }
+}
+
+// ------------------------------------------------------------- decode, flat
+// The same arithmetic with the work laid out flat.  The pages of all (token, kv head) items of the
+// step form one sequence of length total; block c takes pages [c * chunk, (c + 1) * chunk) of it,
+// chunk = ceil(total / blocks), whatever items they belong to.  The grid is one resident wave (two
+// blocks per SM), so that every SM streams the same number of pages whether the batch holds one long
+// sequence or many of unequal lengths.  The producer never drains at an item's end.  An item that one
+// block reads whole is normalised and stored by that block.  Otherwise each block writes its piece
+// (o, m, l) into slot (block + item), which grows along the walk, so blocks + items slots suffice, and
+// counts itself on the item's counter; the block that arrives last merges the pieces in slot order and
+// sets the counter back to zero.  No block waits for another.
+constexpr int FLAT_MAX_TOKENS = 4096;
+
+template <int HD> using FlatCfg = AtcCfg<HD, HD == 128 ? 3 : 5>;
+
+struct FlatSizes {
+    int merge_floats;      // [4 warps][group][HD] + [4][16] + [4][16]
+    int prefix_ints;       // T + 1
+    int smem;
+};
+template <int HD>
+static inline FlatSizes flat_sizes(int group, int T) {
+    FlatSizes z;
+    z.merge_floats = ATC_CONSUMERS * group * HD + 2 * ATC_CONSUMERS * 16;
+    z.prefix_ints = T + 1;
+    z.smem = 1024 + FlatCfg<HD>::STAGES * 2 * FlatCfg<HD>::TILE_BYTES + 256 + 4 * z.merge_floats + 4 * z.prefix_ints;
+    return z;
+}
+
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(ATC_CONSUMERS * 32) : "memory"); }
+
+// Barrier of the consumer warps that also tells every one of them whether any passed true.
+__device__ __forceinline__ bool bar_consumers_or(bool v) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"((uint32_t)v), "n"(ATC_CONSUMERS * 32) : "memory");
+    return r != 0;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(ATC_THREADS, 2)
+attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                        AtcCommon a, const int* __restrict__ positions, const int* __restrict__ seq_of_token, int T,
+                        int* __restrict__ counters, float* __restrict__ slots, __nv_bfloat16* __restrict__ out) {
+    using C = FlatCfg<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t k0 = base, v0 = base + C::STAGES * C::TILE_BYTES;
+    const uint32_t bar = v0 + C::STAGES * C::TILE_BYTES;
+    const uint32_t full0 = bar, empty0 = bar + 8 * C::STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (bar - base) + 16 * C::STAGES);
+    const int group = a.n_heads / a.n_kv;
+    float* mo = reinterpret_cast<float*>(smem + (bar - base) + 256);           // [4][group][HD]
+    float* mm = mo + ATC_CONSUMERS * group * HD;                                // [4][16]
+    float* ml = mm + ATC_CONSUMERS * 16;                                        // [4][16]
+    int* pre = reinterpret_cast<int*>(ml + ATC_CONSUMERS * 16);                 // [T + 1] pages before token t
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmap_k);
+        prefetch_tmap(&tmap_v);
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, ATC_CONSUMERS);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    // Positions and block tables are written by the host's copy before the step's first kernel, not by
+    // the kernel before this one: they may be read before the wait below.
+    for (int t = threadIdx.x; t < T; t += blockDim.x) {
+        const int pos = positions[t];
+        const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+        pre[t + 1] = pos / PAGE + 1 - start / PAGE;
+    }
+    if (threadIdx.x == 0) pre[0] = 0;
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int b0 = 0; b0 < T; b0 += 32) {
+            int v = b0 + lane < T ? pre[b0 + lane + 1] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += u;
+            }
+            if (b0 + lane < T) pre[b0 + lane + 1] = v + carry;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    const long total = (long)pre[T] * a.n_kv;
+    const long chunk = max(1L, (total + gridDim.x - 1) / gridDim.x);
+    const long g0 = (long)blockIdx.x * chunk, g1 = min(total, g0 + chunk);
+    if (g0 >= total) return;
+    // the token whose pages hold g0: the last t with n_kv * pre[t] <= g0
+    int t0 = 0;
+    {
+        int lo = 0, hi = T - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if ((long)pre[mid] * a.n_kv <= g0) lo = mid; else hi = mid - 1;
+        }
+        t0 = lo;
+    }
+    const int p0 = pre[t0 + 1] - pre[t0];
+    const int rem0 = (int)(g0 - (long)pre[t0] * a.n_kv);
+    const int kvh0 = rem0 / p0, j0 = rem0 - kvh0 * p0;
+
+    if (warp == ATC_CONSUMERS) {
+        // ---- producer: the whole warp fetches block-table entries, lane 0 issues the copies
+        // Only the page that holds a sequence's newest position was written by the kernel before this one
+        // (the step's keys and values); every other page is older than the step and is requested at once.
+        int t = t0, kvh = kvh0, j = j0, issued = 0;
+        long g = g0;
+        bool alive = true, waited = false;
+        while (g < g1 && alive) {
+            const int p_t = pre[t + 1] - pre[t];
+            const int seg = (int)min((long)(p_t - j), g1 - g);
+            const int pos = positions[t];
+            const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+            const int* bt = a.block_table + (long)seq_of_token[t] * a.bt_stride + start / PAGE + j;
+            const int i_new = p_t - 1 - j;               // index within this run of the page of position pos
+            for (int i0 = 0; i0 < seg && alive; i0 += 32) {
+                const int mine = i0 + lane < seg ? bt[i0 + lane] : 0;
+                const int n = min(32, seg - i0);
+                for (int i = 0; i < n; ++i, ++issued) {
+                    const int page = __shfl_sync(0xffffffffu, mine, i);
+                    int ok = 1;
+                    if (lane == 0) {
+                        const int s = issued % C::STAGES;
+                        const uint32_t ph = (issued / C::STAGES) & 1;
+                        ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, a.err, ERR_ATT_EMPTY) ? 1 : 0;
+                        if (ok) {
+                            if (!waited && i0 + i == i_new) { pdl_wait(); waited = true; }
+                            const int row = (page * a.n_kv + kvh) * PAGE;
+                            mbar_expect_tx(full0 + 8 * s, 2 * C::TILE_BYTES);
+#pragma unroll
+                            for (int b = 0; b < HD / 64; ++b) {
+                                tma_load_2d(k0 + s * C::TILE_BYTES + b * 8192, &tmap_k, full0 + 8 * s, b * 64, row);
+                                tma_load_2d(v0 + s * C::TILE_BYTES + b * 8192, &tmap_v, full0 + 8 * s, b * 64, row);
+                            }
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) { alive = false; break; }
+                }
+            }
+            g += seg;
+            j += seg;
+            if (j == p_t) { j = 0; if (++kvh == a.n_kv) { kvh = 0; ++t; } }
+        }
+        if (lane == 0 && *abort_flag) {
+            const int first = issued > C::STAGES ? issued - C::STAGES : 0;
+            for (int i = first; i < issued; ++i) {
+                bool landed = false;
+                for (uint32_t n = 0; n < WAIT_POLLS && !landed; ++n)
+                    landed = mbar_try_wait(full0 + 8 * (i % C::STAGES), (i / C::STAGES) & 1);
+                if (!landed && a.err) atomicCAS(a.err, 0, ERR_WAIT_DRAIN);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers
+    pdl_wait();
+    const int gid = lane >> 2, tid4 = lane & 3;
+    // a slot: [group][HD] sums, then [group][2] (maximum, denominator); slots start on 16-byte boundaries
+    const long slot_floats = ((long)group * (HD + 2) + 3) / 4 * 4;
+    int t = t0, kvh = kvh0, j = j0, it = 0;
+    long g = g0;
+    while (g < g1) {
+        const int p_t = pre[t + 1] - pre[t];
+        const int seg = (int)min((long)(p_t - j), g1 - g);
+        const int pos = positions[t];
+        const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+        const int first_page = start / PAGE;
+        const __nv_bfloat16* qrow = a.q + (long)t * a.q_row_stride + (long)kvh * group * HD;
+        uint32_t qf[HD / 16][4];
+        load_q_frags<HD>(qf, gid < group ? qrow + gid * HD : nullptr, gid + 8 < group ? qrow + (gid + 8) * HD : nullptr,
+                         tid4);
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[HD / 8][4];
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
+        for (int i = 0; i < seg; ++i, ++it) {
+            const int s = it % C::STAGES;
+            if (!mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL)) break;
+            const int p = first_page + j + i;
+            if (p * PAGE >= start && p * PAGE + PAGE - 1 <= pos)
+                page_step<HD, 2, true>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
+                                       pos, pos, start, start, a.scale_log2, m, l, o, lane);
+            else
+                page_step<HD, 2, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
+                                        pos, pos, start, start, a.scale_log2, m, l, o, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+            l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+        }
+        // the four warps each saw a quarter of the keys of every page: through shared memory, rows < group only
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            const int d = n * 8 + 2 * tid4;
+            if (gid < group) { float* r0 = mo + (warp * group + gid) * HD + d; r0[0] = o[n][0]; r0[1] = o[n][1]; }
+            if (gid + 8 < group) { float* r1 = mo + (warp * group + gid + 8) * HD + d; r1[0] = o[n][2]; r1[1] = o[n][3]; }
+        }
+        if (tid4 == 0) {
+            mm[warp * 16 + gid] = m[0]; mm[warp * 16 + gid + 8] = m[1];
+            ml[warp * 16 + gid] = l[0]; ml[warp * 16 + gid + 8] = l[1];
+        }
+        const bool dead = bar_consumers_or(*abort_flag != 0);          // the same answer in every warp
+        const int item = t * a.n_kv + kvh;
+        const long s_i = (long)pre[t] * a.n_kv + (long)kvh * p_t;        // where the item's pages begin
+        const int first_block = (int)(s_i / chunk);
+        const int pieces = (int)((s_i + p_t - 1) / chunk) - first_block + 1;
+        __nv_bfloat16* orow = out + ((long)t * a.n_heads + (long)kvh * group) * HD;
+        if (!dead) {
+            float* slot = slots + (long)(blockIdx.x + item) * slot_floats;
+            for (int idx = threadIdx.x; idx < group * HD; idx += ATC_CONSUMERS * 32) {
+                const int r = idx / HD, d = idx - r * HD;
+                float big = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < ATC_CONSUMERS; ++w) big = fmaxf(big, mm[w * 16 + r]);
+                float acc = 0.f, den = 0.f;
+#pragma unroll
+                for (int w = 0; w < ATC_CONSUMERS; ++w) {
+                    const float mw = mm[w * 16 + r];
+                    const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - big);
+                    acc += mo[(w * group + r) * HD + d] * wgt;
+                    den += ml[w * 16 + r] * wgt;
+                }
+                if (pieces == 1) {
+                    orow[r * HD + d] = __float2bfloat16_rn(acc / den);
+                } else {
+                    slot[idx] = acc;
+                    if (d == 0) { slot[group * HD + 2 * r] = big; slot[group * HD + 2 * r + 1] = den; }
+                }
+            }
+        }
+        if (pieces > 1 && !dead) {
+            __threadfence();                       // this thread's part of the piece is visible to the GPU
+            bar_consumers();
+            bool last = false;
+            if (threadIdx.x == 0) {
+                last = atomicAdd(&counters[item], 1) == pieces - 1;
+                if (last) counters[item] = 0;      // every piece has arrived: ready for the next call
+            }
+            last = bar_consumers_or(last);
+            if (last) {
+                __threadfence();
+                const float* first = slots + (long)(first_block + item) * slot_floats;
+                const long step = slot_floats;
+                if (pieces <= 2 * HD) {
+                    // (m, l) of every piece in one round of loads, turned into weights 2^(m - M) / L in place
+                    float* wm = mo;                                    // [group][pieces]
+                    float* wl = mo + group * pieces;
+                    for (int i = threadIdx.x; i < group * pieces; i += ATC_CONSUMERS * 32) {
+                        const int r = i / pieces, sidx = i - r * pieces;
+                        const float2 v = __ldcg(reinterpret_cast<const float2*>(first + sidx * step + group * HD + 2 * r));
+                        wm[i] = v.x;
+                        wl[i] = v.y;
+                    }
+                    bar_consumers();
+                    if (threadIdx.x < group) {
+                        const int r = threadIdx.x;
+                        float big = -INFINITY, den = 0.f;
+                        for (int sidx = 0; sidx < pieces; ++sidx) big = fmaxf(big, wm[r * pieces + sidx]);
+                        for (int sidx = 0; sidx < pieces; ++sidx) {
+                            const float mv = wm[r * pieces + sidx];
+                            den += mv == -INFINITY ? 0.f : wl[r * pieces + sidx] * exp2f(mv - big);
+                        }
+                        mm[r] = big;
+                        ml[r] = 1.f / den;
+                    }
+                    bar_consumers();
+                    for (int i = threadIdx.x; i < group * pieces; i += ATC_CONSUMERS * 32) {
+                        const int r = i / pieces;
+                        const float mv = wm[i];
+                        wm[i] = mv == -INFINITY ? 0.f : exp2f(mv - mm[r]) * ml[r];
+                    }
+                    bar_consumers();
+                    // four neighbouring sums of a row per load, eight pieces in flight
+                    for (int f = threadIdx.x; f < group * HD / 4; f += ATC_CONSUMERS * 32) {
+                        const int r = f / (HD / 4);
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int s0 = 0; s0 < pieces; s0 += 8) {
+                            float4 v[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u)
+                                v[u] = s0 + u < pieces ? __ldcg(reinterpret_cast<const float4*>(first + (s0 + u) * step) + f)
+                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const float w = s0 + u < pieces ? wm[r * pieces + s0 + u] : 0.f;
+                                acc.x += v[u].x * w; acc.y += v[u].y * w; acc.z += v[u].z * w; acc.w += v[u].w * w;
+                            }
+                        }
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(orow + 4 * f) = packed;
+                    }
+                } else {
+                    // more pieces than the merge area holds weights for: straight from global memory
+                    for (int idx = threadIdx.x; idx < group * HD; idx += ATC_CONSUMERS * 32) {
+                        const int r = idx / HD, d = idx - r * HD;
+                        const float* ml_r = first + group * HD + 2 * r;
+                        float big = -INFINITY;
+                        for (int sidx = 0; sidx < pieces; ++sidx) big = fmaxf(big, __ldcg(ml_r + sidx * step));
+                        float acc = 0.f, den = 0.f;
+                        for (int sidx = 0; sidx < pieces; ++sidx) {
+                            const float mv = __ldcg(ml_r + sidx * step);
+                            const float wgt = mv == -INFINITY ? 0.f : exp2f(mv - big);
+                            acc += __ldcg(first + sidx * step + idx) * wgt;
+                            den += __ldcg(ml_r + sidx * step + 1) * wgt;
+                        }
+                        orow[r * HD + d] = __float2bfloat16_rn(acc / den);
+                    }
+                }
+            }
+        }
+        bar_consumers();                           // the merge area is free for the next item
+        if (dead) break;
+        g += seg;
+        j += seg;
+        if (j == p_t) { j = 0; if (++kvh == a.n_kv) { kvh = 0; ++t; } }
     }
 }
 
@@ -402,8 +741,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         fence_mbar_init();
     }
     __syncthreads();
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == ATC_CONSUMERS) {
         if (lane == 0)
@@ -605,6 +944,79 @@ ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out,
                            (const float*)part_ml, (__nv_bfloat16*)out, n_splits);
         if (e != cudaSuccess) return (int)e;
     }
+    return launch_status();
+}
+
+// Decode attention with the pages of the whole step divided evenly over one resident wave of blocks.
+//   n_blocks  0: two blocks (or what fits) per SM; else that many blocks
+//   scratch   floats for zlm_attention_decode_flat_scratch(...) of the same arguments
+namespace zlm {
+template <int HD>
+static int flat_blocks(int group, int T, int* smem_out) {
+    const FlatSizes z = flat_sizes<HD>(group, T);
+    if (smem_out) *smem_out = z.smem;
+    if (z.smem > 227 * 1024) return 0;
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    static int configured = 0;
+    if (configured < z.smem) {
+        if (cudaFuncSetAttribute(attn_decode_flat_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+            cudaSuccess) return 0;
+        if (cudaFuncSetAttribute(attn_decode_flat_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess) return 0;
+        configured = 227 * 1024;
+    }
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_flat_kernel<HD>, ATC_THREADS, z.smem) !=
+        cudaSuccess) return 0;
+    return sms * min(per_sm, 2);
+}
+}  // namespace zlm
+
+ZLM_EXPORT int zlm_attention_decode_flat_blocks(int T, int n_heads, int n_kv, int hd) {
+    if (T <= 0 || T > FLAT_MAX_TOKENS || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || n_heads / n_kv > 16) return 0;
+    if (hd == 128) return flat_blocks<128>(n_heads / n_kv, T, nullptr);
+    if (hd == 64) return flat_blocks<64>(n_heads / n_kv, T, nullptr);
+    return 0;
+}
+
+// Floats of piece storage the flat kernel needs with n_blocks blocks.  Beside it the caller keeps T * n_kv
+// int counters that are zero before the first call; every call that completes leaves them zero.
+ZLM_EXPORT long zlm_attention_decode_flat_scratch(int T, int n_heads, int n_kv, int hd, int n_blocks) {
+    if (T <= 0 || n_kv <= 0 || n_heads <= 0 || n_blocks <= 0) return 0;
+    const long slot = ((long)(n_heads / n_kv) * (hd + 2) + 3) / 4 * 4;
+    return ((long)n_blocks + (long)T * n_kv) * slot;
+}
+
+ZLM_EXPORT int zlm_attention_decode_flat(const void* q, long q_row_stride, void* out, int T, int n_heads, int n_kv,
+                                         int hd, float scale, int window, const int* positions,
+                                         const int* seq_of_token, const int* block_table, int bt_stride,
+                                         const void* k_pages, const void* v_pages, long n_pages, int page_size,
+                                         int n_blocks, int* counters, float* scratch, long scratch_floats,
+                                         cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (T > FLAT_MAX_TOKENS) return ZLM_ERR_UNSUPPORTED;
+    if (n_kv > 0 && n_heads / n_kv > 16) return ZLM_ERR_UNSUPPORTED;
+    AtcCommon a;
+    CUtensorMap mk, mv;
+    int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
+                         k_pages, v_pages, n_pages, page_size);
+    if (rc) return rc;
+    const int group = n_heads / n_kv;
+    int smem = 0;
+    const int resident = hd == 128 ? flat_blocks<128>(group, T, &smem) : flat_blocks<64>(group, T, &smem);
+    if (resident <= 0) return ZLM_ERR_UNSUPPORTED;
+    if (n_blocks <= 0) n_blocks = resident;
+    if (!counters || !scratch || zlm_attention_decode_flat_scratch(T, n_heads, n_kv, hd, n_blocks) > scratch_floats)
+        return ZLM_ERR_BAD_ARG;
+    cudaError_t e;
+    if (hd == 128)
+        e = launch_pdl(attn_decode_flat_kernel<128>, dim3(n_blocks), dim3(ATC_THREADS), (size_t)smem, stream, mk, mv, a,
+                       positions, seq_of_token, T, counters, scratch, (__nv_bfloat16*)out);
+    else
+        e = launch_pdl(attn_decode_flat_kernel<64>, dim3(n_blocks), dim3(ATC_THREADS), (size_t)smem, stream, mk, mv, a,
+                       positions, seq_of_token, T, counters, scratch, (__nv_bfloat16*)out);
+    if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 

@@ -82,9 +82,13 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 // Programmatic dependent launch: a kernel launched with launch_pdl may become resident while the
-// kernel before it in the stream is still running.  It must call pdl_wait() before it reads what
-// that kernel wrote or writes what that kernel read; pdl_launch_dependents() lets the kernel after
-// it become resident in turn.
+// kernels before it in the stream are still running.  It must call pdl_wait() before it reads what
+// a kernel of the same step wrote or writes what one may read; pdl_launch_dependents() lets the
+// kernel after it become resident in turn.  Kernels call it first, so that the next kernel's set-up
+// (and its requests for weights and for cache pages older than the step) overlaps this kernel's
+// work.  pdl_wait() returns when the kernel before has completed, which it cannot do before its own
+// pdl_wait() has returned: what a kernel does after its wait sees every earlier kernel complete.
+// What it does before the wait may touch only memory that no kernel of the step writes.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

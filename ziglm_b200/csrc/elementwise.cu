@@ -17,8 +17,8 @@ namespace zlm {
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int d, float scale) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const long row = (long)tokens[t] * d;
     float* o = out + (long)t * d;
@@ -57,8 +57,8 @@ template <typename TW, typename TO, bool VEC>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int d, float eps, float weight_offset) {
     __shared__ float scratch[33];
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (long)(rows ? rows[r] : r) * d;
     TO* o = out + (long)r * d;
@@ -118,8 +118,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
 template <typename T>
 __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, long total, int I, int kind,
                                  int interleaved) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const long t = idx / I;

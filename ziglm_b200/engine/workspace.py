@@ -17,14 +17,17 @@ class Workspace:
         self.device = device
         self._flat: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
 
-    def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+    def buf(self, name: str, shape, dtype: torch.dtype, zeros: bool = False) -> torch.Tensor:
+        """The named buffer, at least as large as ``shape``.  ``zeros``: the memory is zero when it is first
+        handed out (and when it has grown); afterwards it holds what its users left."""
         n = 1
         for s in shape:
             n *= int(s)
         key = (name, dtype)
         flat = self._flat.get(key)
         if flat is None or flat.numel() < n:
-            flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            make = torch.zeros if zeros else torch.empty
+            flat = make(max(n, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
         return flat[:n].view(*shape)
 

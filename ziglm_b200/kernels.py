@@ -70,6 +70,11 @@ _PROTOTYPES = {
         "zlm_attention_decode": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                  c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
                                  c_void_p, c_void_p],
+        "zlm_attention_decode_flat": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
+                                      c_void_p, c_long, c_void_p],
+        "zlm_attention_decode_flat_blocks": [c_int, c_int, c_int, c_int],
+        "zlm_attention_decode_flat_scratch": [c_int, c_int, c_int, c_int, c_int],
         "zlm_attention_prefill": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "zlm_attention_tc_status": [c_void_p],
@@ -100,7 +105,7 @@ def _fn(library: str, name: str):
         lib = _build.load(library)
         f = getattr(lib, name)
         f.argtypes = _PROTOTYPES[library][name]
-        f.restype = c_int
+        f.restype = c_long if name.endswith("_scratch") else c_int
         _functions[name] = f
     return f
 
@@ -325,6 +330,56 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: i
     return True
 
 
+def attention_decode_flat_blocks(n_tokens: int, n_heads: int, n_kv: int, head_dim: int) -> int:
+    """Blocks of one resident wave of the flat decode kernel for a step of ``n_tokens`` (0: sizes it refuses)."""
+    return int(_fn("attention_tc", "zlm_attention_decode_flat_blocks")(n_tokens, n_heads, n_kv, head_dim))
+
+
+def attention_decode_flat_scratch(n_tokens: int, n_heads: int, n_kv: int, head_dim: int, n_blocks: int) -> int:
+    """Floats of scratch the flat decode kernel needs with ``n_blocks`` blocks."""
+    return int(_fn("attention_tc", "zlm_attention_decode_flat_scratch")(n_tokens, n_heads, n_kv, head_dim, n_blocks))
+
+
+def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
+                          window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
+                          block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int,
+                          n_blocks: int, counters: torch.Tensor, scratch: torch.Tensor) -> bool:
+    """Tensor-core attention for steps of one token per sequence, with the pages of all sequences of the
+    step divided evenly over ``n_blocks`` blocks (one resident wave), whatever the sequences' lengths.  One
+    launch: the block that finishes a sequence's last piece merges the pieces.
+
+    ``scratch``: float32, at least ``attention_decode_flat_scratch(...)`` elements, any content.
+    ``counters``: int32, one per (token, kv head), zero before the first call; a call that completes leaves
+    them zero (a call that ended with a wait error does not: zero them again).  False if refused.
+    """
+    _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
+    _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
+    _cuda(block_table, "block_table", torch.int32); _cuda(scratch, "scratch", torch.float32)
+    _cuda(counters, "counters", torch.int32)
+    T = out.shape[0]
+    if counters.numel() < T * n_kv:
+        raise KernelError("attention_decode_flat: one counter per (token, kv head) is needed")
+    if not qkv.is_cuda or qkv.dtype != torch.bfloat16 or qkv.stride(1) != 1:
+        raise KernelError("attention_decode_flat: q must be bfloat16 on the device with unit column stride")
+    if out.shape[1] != n_heads * head_dim or qkv.shape[1] < n_heads * head_dim or qkv.shape[0] < T:
+        raise KernelError("attention_decode_flat: widths do not match the head counts")
+    if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError("attention_decode_flat: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+    if n_blocks <= 0:
+        raise KernelError("attention_decode_flat: the number of blocks must be positive")
+    status = _fn("attention_tc", "zlm_attention_decode_flat")(
+        qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, int(window or 0),
+        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+        k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_blocks, counters.data_ptr(),
+        scratch.data_ptr(), scratch.numel(), _stream())
+    if status == -2:
+        return False
+    if status == -1:
+        raise KernelError("attention_decode_flat: bad arguments, or the scratch is too small for this many blocks")
+    _check(status, "attention_decode_flat")
+    return True
+
+
 def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, n_kv: int,
                       head_dim: int, scale: float, window: Optional[int], cu_seqlens: torch.Tensor,
                       past_lens: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
@@ -410,6 +465,15 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
               window: Optional[int], io) -> None:
     """Attention of a step's tokens over the cache of the running layer; picks the kernel."""
     if _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
+        n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim) if step.single_token else 0
+        if n_blocks > 0:
+            need = attention_decode_flat_scratch(step.n_tokens, n_heads, n_kv, head_dim, n_blocks)
+            scratch = step.ws.buf("attn_flat_scratch", (need,), torch.float32)
+            counters = step.ws.buf("attn_flat_counters", (step.n_tokens * n_kv,), torch.int32, zeros=True)
+            if attention_decode_flat(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions,
+                                     step.seq_of_token, io.block_table, io.k_pages, io.v_pages, io.page_size,
+                                     n_blocks, counters, scratch):
+                return
         if step.single_token:
             n_splits = decode_splits(step.n_tokens, n_kv, step.max_total, io.page_size)
             part_o = step.ws.buf("attn_part_o", (step.n_tokens * n_heads * n_splits * head_dim,), torch.float32)
