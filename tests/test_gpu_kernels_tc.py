@@ -168,6 +168,56 @@ def test_attention_decode_flat_many_tokens(K):
     assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("hd,rot", [(64, 64), (128, 128), (128, 64), (64, 0)])
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (6, 3)])
+@pytest.mark.parametrize("store", [True, False])
+@pytest.mark.parametrize("n_blocks", [0, 5])
+def test_attention_decode_flat_with_rotation_and_cache_write(K, hd, rot, nh, nkv, store, n_blocks):
+    """The flat kernel doing the step's rotation and cache write itself, against rope_store followed by the
+    same kernel without them: the same output, the same rows in the cache, qkv left as it was.  Positions at
+    the start, the end and the middle of a page; the cache row of the new token holds poison beforehand."""
+    lens_past = [0, 130, 63, 300, 64, 1000, 5, 127]
+    T = len(lens_past)
+    ks = [rnd((p + 1, nkv, hd), BF, seed=50 + 10 * b) for b, p in enumerate(lens_past)]
+    vs = [rnd((p + 1, nkv, hd), BF, seed=51 + 10 * b) for b, p in enumerate(lens_past)]
+    kp, vp, table = paged(ks, vs, 64, BF, seed=4)
+    for b, p in enumerate(lens_past):                       # the new token is not in the cache yet
+        kp[table[b, p // 64], :, p % 64] = 777.0
+        vp[table[b, p // 64], :, p % 64] = -777.0
+    width = (nh + (2 * nkv if store else 0)) * hd
+    qkv = rnd((T, width), BF, seed=60).to(DEV)
+    inv = P.rope_inverse_frequencies(rot, 500000.0, None).to(device=DEV, dtype=torch.float32) if rot else None
+    positions = torch.tensor(lens_past, dtype=torch.int32, device=DEV)
+    seq = torch.arange(T, dtype=torch.int32, device=DEV)
+    table = table.to(DEV)
+    scale = 1.0 / math.sqrt(hd)
+    nb = n_blocks or K.attention_decode_flat_blocks(T, nh, nkv, hd)
+
+    def run(fused):
+        k_pages, v_pages, rows = kp.to(DEV), vp.to(DEV), qkv.clone()
+        if not store:                                       # somebody else has written the new rows already
+            for b, p in enumerate(lens_past):
+                k_pages[table[b, p // 64], :, p % 64] = ks[b][p].to(DEV)
+                v_pages[table[b, p // 64], :, p % 64] = vs[b][p].to(DEV)
+        out = torch.zeros(T, nh * hd, dtype=BF, device=DEV)
+        scratch = torch.full((K.attention_decode_flat_scratch(T, nh, nkv, hd, nb),), float("nan"), device=DEV)
+        counters = torch.zeros(T * nkv, dtype=torch.int32, device=DEV)
+        if not fused:
+            K.rope_store(rows, nh, nkv if store else 0, hd, rot, inv, positions, seq, table,
+                         k_pages if store else None, v_pages if store else None, 64)
+        assert K.attention_decode_flat(rows, out, nh, nkv, hd, scale, None, positions, seq, table, k_pages, v_pages,
+                                       64, nb, counters, scratch, rope=(inv, rot, store) if fused else None)
+        torch.cuda.synchronize()
+        assert K.attention_tc_status() == 0 and int(counters.abs().sum()) == 0
+        return out, k_pages, v_pages, rows
+
+    out_f, k_f, v_f, rows_f = run(True)
+    out_u, k_u, v_u, _ = run(False)
+    assert torch.equal(rows_f, qkv)
+    assert torch.equal(k_f, k_u) and torch.equal(v_f, v_u)
+    assert torch.allclose(out_f.float(), out_u.float(), atol=1e-2, rtol=1e-2)
+
+
 @pytest.mark.parametrize("kernel", ["mma", "fmha"])
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("nh,nkv", [(8, 2), (4, 4), (16, 1)])

@@ -400,11 +400,57 @@ __device__ __forceinline__ bool bar_consumers_or(bool v) {
     return r != 0;
 }
 
+// What the flat kernel does for the step's new token itself when the rotation and the cache write are
+// not left to a kernel before it.  The rows of q are then [q heads | k heads | v heads] as the fused
+// projection left them: the block rotates the query heads as it loads them, and the block that reads
+// the page of a sequence's newest position rotates the new key, puts key and value into the page in
+// shared memory and into the cache.  rot is a multiple of 32 (pairs (i, i + rot/2) stay in one thread).
+struct FlatRope {
+    int fused;                 // 0: q is rotated and the cache is complete
+    int store;                 // this layer owns the cache: write the new key and value
+    int rot;                   // rotated width (0: no rotation)
+    const float* inv_freq;     // [rot / 2]
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+};
+
+// Rotate the fragments of 16 query rows in registers: column c of a fragment pairs with c + rot/2,
+// which lies HP = rot/32 fragments further in the same thread and the same register.
+template <int HD, int HP>
+__device__ __forceinline__ void rotate_q_frags_by(uint32_t (&qf)[HD / 16][4], const float* cs, const float* sn, int tid4) {
+#pragma unroll
+    for (int ks = 0; ks < HP; ++ks) {
+#pragma unroll
+        for (int slot = 0; slot < 4; ++slot) {
+            const int c = ks * 16 + 2 * tid4 + (slot >= 2 ? 8 : 0);
+            const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qf[ks][slot]));
+            const float2 y = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qf[ks + HP][slot]));
+            const float c0 = cs[c], s0 = sn[c], c1 = cs[c + 1], s1 = sn[c + 1];
+            qf[ks][slot] = pack_bf16(x.x * c0 - y.x * s0, x.y * c1 - y.y * s1);
+            qf[ks + HP][slot] = pack_bf16(x.x * s0 + y.x * c0, x.y * s1 + y.y * c1);
+        }
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ void rotate_q_frags(uint32_t (&qf)[HD / 16][4], const float* cs, const float* sn, int half,
+                                               int tid4) {
+    switch (half / 16) {
+        case 1: rotate_q_frags_by<HD, 1>(qf, cs, sn, tid4); break;
+        case 2: rotate_q_frags_by<HD, 2>(qf, cs, sn, tid4); break;
+        case 3: if constexpr (HD >= 96) rotate_q_frags_by<HD, 3>(qf, cs, sn, tid4); break;
+        case 4: if constexpr (HD >= 128) rotate_q_frags_by<HD, 4>(qf, cs, sn, tid4); break;
+        default: break;
+    }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(ATC_THREADS, 2)
 attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                        AtcCommon a, const int* __restrict__ positions, const int* __restrict__ seq_of_token, int T,
-                        int* __restrict__ counters, float* __restrict__ slots, __nv_bfloat16* __restrict__ out) {
+                        AtcCommon a, FlatRope rope, const int* __restrict__ positions,
+                        const int* __restrict__ seq_of_token, int T, int* __restrict__ counters,
+                        float* __restrict__ slots, __nv_bfloat16* __restrict__ out) {
+    __shared__ float cs_s[HD / 2], sn_s[HD / 2];
     using C = FlatCfg<HD>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -479,7 +525,8 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         // (the step's keys and values); every other page is older than the step and is requested at once.
         int t = t0, kvh = kvh0, j = j0, issued = 0;
         long g = g0;
-        bool alive = true, waited = false;
+        bool alive = true;
+        bool waited = rope.fused && rope.store;      // the newest key and value are put in by this kernel itself
         while (g < g1 && alive) {
             const int p_t = pre[t + 1] - pre[t];
             const int seg = (int)min((long)(p_t - j), g1 - g);
@@ -533,7 +580,8 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     const int gid = lane >> 2, tid4 = lane & 3;
     // a slot: [group][HD] sums, then [group][2] (maximum, denominator); slots start on 16-byte boundaries
     const long slot_floats = ((long)group * (HD + 2) + 3) / 4 * 4;
-    int t = t0, kvh = kvh0, j = j0, it = 0;
+    const int half = rope.fused ? rope.rot / 2 : 0;
+    int t = t0, kvh = kvh0, j = j0, it = 0, t_angles = -1;
     long g = g0;
     while (g < g1) {
         const int p_t = pre[t + 1] - pre[t];
@@ -541,10 +589,19 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         const int pos = positions[t];
         const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
         const int first_page = start / PAGE;
+        if (half > 0 && t != t_angles) {
+            // cosines and sines of this token's position (float32 angles, as the separate kernel forms them)
+            if (t_angles >= 0) bar_consumers();
+            for (int i = threadIdx.x; i < half; i += ATC_CONSUMERS * 32)
+                sincosf((float)pos * rope.inv_freq[i], &sn_s[i], &cs_s[i]);
+            bar_consumers();
+            t_angles = t;
+        }
         const __nv_bfloat16* qrow = a.q + (long)t * a.q_row_stride + (long)kvh * group * HD;
         uint32_t qf[HD / 16][4];
         load_q_frags<HD>(qf, gid < group ? qrow + gid * HD : nullptr, gid + 8 < group ? qrow + (gid + 8) * HD : nullptr,
                          tid4);
+        if (half > 0) rotate_q_frags<HD>(qf, cs_s, sn_s, half, tid4);
         float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
         float o[HD / 8][4];
 #pragma unroll
@@ -553,8 +610,41 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
             for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
         for (int i = 0; i < seg; ++i, ++it) {
             const int s = it % C::STAGES;
-            if (!mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL)) break;
+            bool landed = mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL);
             const int p = first_page + j + i;
+            if (rope.fused && rope.store && j + i == p_t - 1) {
+                // The page of position pos: its row pos % 64 is not in the cache yet.  The new key (rotated)
+                // and value go into the page in shared memory and into the cache, then everybody reads.
+                landed = !bar_consumers_or(!landed);
+                if (landed) {
+                    const int r = pos % PAGE;
+                    const __nv_bfloat16* knew = a.q + (long)t * a.q_row_stride + (long)(a.n_heads + kvh) * HD;
+                    const __nv_bfloat16* vnew = knew + (long)a.n_kv * HD;
+                    const long crow = ((long)a.block_table[(long)seq_of_token[t] * a.bt_stride + p] * a.n_kv + kvh) * PAGE + r;
+                    __nv_bfloat16* kdst = rope.k_pages + crow * HD;
+                    __nv_bfloat16* vdst = rope.v_pages + crow * HD;
+                    uint8_t* ktile = smem + (k0 + s * C::TILE_BYTES - base);
+                    uint8_t* vtile = smem + (v0 + s * C::TILE_BYTES - base);
+                    for (int d = threadIdx.x; d < HD; d += ATC_CONSUMERS * 32) {
+                        __nv_bfloat16 kv;
+                        if (d < 2 * half) {
+                            const int ii = d < half ? d : d - half;
+                            const float x = __bfloat162float(knew[ii]), y = __bfloat162float(knew[ii + half]);
+                            kv = __float2bfloat16_rn(d < half ? x * cs_s[ii] - y * sn_s[ii] : x * sn_s[ii] + y * cs_s[ii]);
+                        } else {
+                            kv = knew[d];
+                        }
+                        const __nv_bfloat16 vv = vnew[d];
+                        const uint32_t off = tile_addr(0u, r, d >> 3) + (d & 7) * 2;
+                        *reinterpret_cast<__nv_bfloat16*>(ktile + off) = kv;
+                        *reinterpret_cast<__nv_bfloat16*>(vtile + off) = vv;
+                        kdst[d] = kv;
+                        vdst[d] = vv;
+                    }
+                }
+                bar_consumers();
+            }
+            if (!landed) break;
             if (p * PAGE >= start && p * PAGE + PAGE - 1 <= pos)
                 page_step<HD, 2, true>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
                                        pos, pos, start, start, a.scale_log2, m, l, o, lane);
@@ -955,18 +1045,25 @@ template <int HD>
 static int flat_blocks(int group, int T, int* smem_out) {
     const FlatSizes z = flat_sizes<HD>(group, T);
     if (smem_out) *smem_out = z.smem;
-    if (z.smem > 227 * 1024) return 0;
     int dev = 0, sms = 0, per_sm = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    static int configured = 0;
-    if (configured < z.smem) {
-        if (cudaFuncSetAttribute(attn_decode_flat_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
-            cudaSuccess) return 0;
-        if (cudaFuncSetAttribute(attn_decode_flat_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess) return 0;
-        configured = 227 * 1024;
+    static int max_dynamic = 0;
+    if (max_dynamic == 0) {
+        // the kernel's static shared memory counts against the same 227 KB
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, attn_decode_flat_kernel<HD>) != cudaSuccess) { cudaGetLastError(); return 0; }
+        const int room = 227 * 1024 - (int)fa.sharedSizeBytes;
+        if (cudaFuncSetAttribute(attn_decode_flat_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, room) !=
+                cudaSuccess ||
+            cudaFuncSetAttribute(attn_decode_flat_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
+        max_dynamic = room;
     }
+    if (z.smem > max_dynamic) return 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_flat_kernel<HD>, ATC_THREADS, z.smem) !=
         cudaSuccess) return 0;
     return sms * min(per_sm, 2);
@@ -993,10 +1090,19 @@ ZLM_EXPORT int zlm_attention_decode_flat(const void* q, long q_row_stride, void*
                                          const int* seq_of_token, const int* block_table, int bt_stride,
                                          const void* k_pages, const void* v_pages, long n_pages, int page_size,
                                          int n_blocks, int* counters, float* scratch, long scratch_floats,
+                                         int rope_fused, int rope_store, int rot, const float* inv_freq,
                                          cudaStream_t stream) {
     if (T <= 0) return 0;
     if (T > FLAT_MAX_TOKENS) return ZLM_ERR_UNSUPPORTED;
     if (n_kv > 0 && n_heads / n_kv > 16) return ZLM_ERR_UNSUPPORTED;
+    if (rope_fused && (rot < 0 || rot > hd || rot % 32 || (rot > 0 && !inv_freq))) return ZLM_ERR_UNSUPPORTED;
+    FlatRope rope;
+    rope.fused = rope_fused ? 1 : 0;
+    rope.store = rope_fused && rope_store ? 1 : 0;
+    rope.rot = rope_fused ? rot : 0;
+    rope.inv_freq = inv_freq;
+    rope.k_pages = (__nv_bfloat16*)const_cast<void*>(k_pages);
+    rope.v_pages = (__nv_bfloat16*)const_cast<void*>(v_pages);
     AtcCommon a;
     CUtensorMap mk, mv;
     int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
@@ -1012,10 +1118,10 @@ ZLM_EXPORT int zlm_attention_decode_flat(const void* q, long q_row_stride, void*
     cudaError_t e;
     if (hd == 128)
         e = launch_pdl(attn_decode_flat_kernel<128>, dim3(n_blocks), dim3(ATC_THREADS), (size_t)smem, stream, mk, mv, a,
-                       positions, seq_of_token, T, counters, scratch, (__nv_bfloat16*)out);
+                       rope, positions, seq_of_token, T, counters, scratch, (__nv_bfloat16*)out);
     else
         e = launch_pdl(attn_decode_flat_kernel<64>, dim3(n_blocks), dim3(ATC_THREADS), (size_t)smem, stream, mk, mv, a,
-                       positions, seq_of_token, T, counters, scratch, (__nv_bfloat16*)out);
+                       rope, positions, seq_of_token, T, counters, scratch, (__nv_bfloat16*)out);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_long, c_void_p
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -72,7 +72,7 @@ _PROTOTYPES = {
                                  c_void_p, c_void_p],
         "zlm_attention_decode_flat": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                       c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
-                                      c_void_p, c_long, c_void_p],
+                                      c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p],
         "zlm_attention_decode_flat_blocks": [c_int, c_int, c_int, c_int],
         "zlm_attention_decode_flat_scratch": [c_int, c_int, c_int, c_int, c_int],
         "zlm_attention_prefill": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
@@ -343,7 +343,8 @@ def attention_decode_flat_scratch(n_tokens: int, n_heads: int, n_kv: int, head_d
 def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
                           window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                           block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int,
-                          n_blocks: int, counters: torch.Tensor, scratch: torch.Tensor) -> bool:
+                          n_blocks: int, counters: torch.Tensor, scratch: torch.Tensor,
+                          rope: Optional[Tuple[Optional[torch.Tensor], int, bool]] = None) -> bool:
     """Tensor-core attention for steps of one token per sequence, with the pages of all sequences of the
     step divided evenly over ``n_blocks`` blocks (one resident wave), whatever the sequences' lengths.  One
     launch: the block that finishes a sequence's last piece merges the pieces.
@@ -351,6 +352,12 @@ def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_
     ``scratch``: float32, at least ``attention_decode_flat_scratch(...)`` elements, any content.
     ``counters``: int32, one per (token, kv head), zero before the first call; a call that completes leaves
     them zero (a call that ended with a wait error does not: zero them again).  False if refused.
+
+    ``rope`` = (inv_freq or None, rotary_dim, store): the kernel also does what ``rope_store`` does for the
+    step's tokens, so that no kernel runs between the projection and the attention.  The rows of ``qkv`` are
+    then [q heads | k heads | v heads] (k and v only with ``store``) as the projection left them; the query
+    heads are rotated as they are loaded (``qkv`` itself is left alone) and, with ``store``, the new keys
+    (rotated) and values go into the cache pages.  rotary_dim must be a multiple of 32.
     """
     _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
     _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
@@ -367,11 +374,23 @@ def attention_decode_flat(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_
         raise KernelError("attention_decode_flat: cache pages must be [n_pages, n_kv, page_size, head_dim]")
     if n_blocks <= 0:
         raise KernelError("attention_decode_flat: the number of blocks must be positive")
+    fused, store, rot, inv_freq = 0, 0, 0, None
+    if rope is not None:
+        inv_freq, rot, store = rope
+        fused = 1
+        if inv_freq is None:
+            rot = 0
+        else:
+            _cuda(inv_freq, "inv_freq", torch.float32)
+            if inv_freq.numel() * 2 != rot:
+                raise KernelError("attention_decode_flat: the frequency table must hold rotary_dim/2 entries")
+        if qkv.shape[1] < (n_heads + (2 * n_kv if store else 0)) * head_dim:
+            raise KernelError("attention_decode_flat: the rows must hold the key and value heads to be stored")
     status = _fn("attention_tc", "zlm_attention_decode_flat")(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, int(window or 0),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
         k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_blocks, counters.data_ptr(),
-        scratch.data_ptr(), scratch.numel(), _stream())
+        scratch.data_ptr(), scratch.numel(), fused, int(bool(store)), int(rot), _ptr(inv_freq), _stream())
     if status == -2:
         return False
     if status == -1:
@@ -459,6 +478,26 @@ def decode_splits(n_tokens: int, n_kv: int, max_total: int, page_size: int = 64)
     pages = max(1, -(-max_total // page_size))
     want = -(-296 // max(1, n_tokens * n_kv))
     return max(1, min(want, pages, 64))
+
+
+def attention_with_rope(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                        scale: float, window: Optional[int], io, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                        store: bool) -> bool:
+    """Decode steps on the tensor-core path: rotation, cache write and attention in one kernel.  False when
+    the step is not of that kind; the caller then runs ``rope_store`` and ``attention``."""
+    if not (step.single_token and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size)):
+        return False
+    if inv_freq is not None and rotary_dim % 32:
+        return False
+    n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim)
+    if n_blocks <= 0:
+        return False
+    need = attention_decode_flat_scratch(step.n_tokens, n_heads, n_kv, head_dim, n_blocks)
+    scratch = step.ws.buf("attn_flat_scratch", (need,), torch.float32)
+    counters = step.ws.buf("attn_flat_counters", (step.n_tokens * n_kv,), torch.int32, zeros=True)
+    return attention_decode_flat(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
+                                 io.block_table, io.k_pages, io.v_pages, io.page_size, n_blocks, counters, scratch,
+                                 rope=(inv_freq, rotary_dim, store))
 
 
 def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,

@@ -99,10 +99,14 @@ class Attention(Part):
         else:
             inv_freq, rot = table
         store = io.writes_cache and not self.shares_cache
+        out = step.ws.buf("attn_out", (T, self.n_heads * self.head_dim), self.dtype)
+        if kernels.attention_with_rope(step, qkv, out, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window,
+                                       io, inv_freq, rot, store):
+            self.o(out, residual, accumulate=True)
+            return
         kernels.rope_store(qkv, self.n_heads, n_kv_here, self.head_dim, rot, inv_freq, step.positions,
                            step.seq_of_token, io.block_table, io.k_pages if store else None,
                            io.v_pages if store else None, io.page_size)
-        out = step.ws.buf("attn_out", (T, self.n_heads * self.head_dim), self.dtype)
         kernels.attention(step, qkv, out, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, io)
         self.o(out, residual, accumulate=True)
 
