@@ -1,20 +1,24 @@
 // Prompt attention over the paged bf16 cache on the 5th-generation tensor cores (tcgen05), head sizes
 // 64 and 128.
 //
-// One block per (tile of 128 queries, head, sequence).  The 128 query rows are the M side of both
-// products, the accumulators live in tensor memory:
-//   S = Q K^T   128 x 128 scores per step of two pages of 64 keys (two buffers, so the next step's
-//               scores are computed while the softmax of this step runs),
-//   O += P V    128 x head_dim.
-// A tcgen05.mma with M = 128 reads its 128 x 16 A operand from shared memory in about 128 cycles
-// whatever its N, so steps are as wide as tensor memory allows: N = 128 keys for the scores.
-// Roles: warp 0 loads Q once and the K/V pages through a ring of stages with TMA (128-byte swizzle);
-// warp 1 issues the tcgen05.mma instructions (K pages are K-major operands, V pages MN-major ones,
-// both exactly as the cache stores them); warps 2-5 are the softmax: thread r owns query row r,
-// reads its row of S with tcgen05.ld, keeps the running maximum and sum in float (base 2, scale
-// folded in), writes the probabilities as bf16 into shared memory as the A operand of P V, and
-// rescales O in tensor memory when its maximum has moved by more than 2^8 (a rescale that is
-// skipped leaves probabilities up to 256, well inside bf16 and float range, and cancels in O / l).
+// One block per (256 consecutive queries, head, sequence): two tiles of 128 query rows that share
+// the K/V pages the block loads.  The 128 rows of a tile are the M side of both products and the
+// accumulators live in tensor memory:
+//   S_t = Q_t K^T    128 x 128 scores per step of two pages of 64 keys,
+//   O_t += P_t V     128 x head_dim, with P_t (bf16) read from tensor memory, where it overwrites S_t.
+// Roles: warp 0 loads Q once and the K and V pages through two rings of stages with TMA (128-byte
+// swizzle; a K stage is free as soon as the scores are computed, a V stage after P V); warp 1 issues
+// the tcgen05.mma instructions (K pages are K-major operands, V pages MN-major ones, both exactly as
+// the cache stores them) in the order  P_0 V, S_0 of the next step, P_1 V, S_1 of the next step, so
+// that the tensor core works for one tile while the softmax of the other runs; warps 2-5 are the
+// softmax of tile 0 and warps 6-9 of tile 1: thread r owns query row r, reads its row of S with
+// tcgen05.ld (twice: for the maximum, then for the exponentials, 32 columns at a time, which keeps
+// registers free), keeps the running maximum and sum in float (base 2, scale folded in), writes the
+// probabilities with tcgen05.st, and rescales O in tensor memory when its maximum has moved by more
+// than 2^8 (a rescale that is skipped leaves probabilities up to 256, well inside bf16 and float
+// range, and cancels in O / l).  The tensor core runs its instructions in the order of issue, so when
+// S_t of a step is there, P_t V of the step before is complete: the softmax may touch O_t and
+// overwrite the old probabilities without another wait.
 // The formulas are those of attention.cu (the reference's src/model.zig:659-700): scores scaled
 // after the dot product, keys [start, pos] visible, softmax with maximum subtraction, weighted sum.
 // Every mbarrier wait is bounded and reports through an error word.
@@ -27,24 +31,26 @@
 namespace zlm {
 using namespace tc;
 
-constexpr int FM_BQ = 128;           // queries per block
+constexpr int FM_BQ = 128;           // query rows of a tile
+constexpr int FM_TILES = 2;          // tiles of a block
+constexpr int FM_ROWS = FM_BQ * FM_TILES;
 constexpr int FM_PAGE = 64;          // keys per page
 constexpr int FM_NP = 2;             // pages per step
 constexpr int FM_KEYS = FM_PAGE * FM_NP;
-constexpr int FM_THREADS = 192;      // TMA warp, MMA warp, four softmax warps
+constexpr int FM_THREADS = 320;      // TMA warp, MMA warp, four softmax warps per tile
 constexpr int ERR_FM_ALIGN = 20, ERR_FM_Q = 21, ERR_FM_KV = 22, ERR_FM_S = 23, ERR_FM_P = 24, ERR_FM_O = 25, ERR_FM_EMPTY = 26;
 
 template <int HD> struct FmCfg {
-    static constexpr int STAGES = 2;
-    static constexpr int Q_BYTES = FM_BQ * HD * 2;
+    static constexpr int NK = 2, NV = 2;                         // stages of the K ring and of the V ring
+    static constexpr int Q_BYTES = FM_BQ * HD * 2;               // one tile of queries
     static constexpr int PAGE_BYTES = FM_PAGE * HD * 2;          // one page of keys (or of values)
     static constexpr int KV_BYTES = FM_NP * PAGE_BYTES;          // the keys (or values) of one step
-    static constexpr int P_BYTES = FM_BQ * FM_KEYS * 2;
     // The kernel checks that its shared memory starts on a 1024-byte boundary (the swizzled tiles need
     // it) and reports an error if it does not.
-    static constexpr int SMEM = Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + 128;
-    static constexpr int S_COL = HD;                             // TMEM columns: O first, then two S buffers
-    static constexpr int TMEM_COLS = HD + 2 * FM_KEYS <= 256 ? 256 : 512;
+    static constexpr int SMEM = FM_TILES * Q_BYTES + (NK + NV) * KV_BYTES + 256;
+    static constexpr int O_COL = 0;                              // TMEM columns: O_0, O_1, then S_0, S_1
+    static constexpr int S_COL = FM_TILES * HD;
+    static constexpr int TMEM_COLS = 512;
 };
 
 // One lane polls the barrier for its warp; 128 threads polling at once slow the barrier unit down.
@@ -80,49 +86,60 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         return;
     }
     const uint32_t q_smem = base;
-    const uint32_t k_smem = q_smem + C::Q_BYTES;
-    const uint32_t v_smem = k_smem + C::STAGES * C::KV_BYTES;
-    const uint32_t p_smem = v_smem + C::STAGES * C::KV_BYTES;
-    const uint32_t bar = p_smem + C::P_BYTES;
+    const uint32_t k_smem = q_smem + FM_TILES * C::Q_BYTES;
+    const uint32_t v_smem = k_smem + C::NK * C::KV_BYTES;
+    const uint32_t bar = v_smem + C::NV * C::KV_BYTES;
     // barriers
     const uint32_t q_full = bar;
-    const uint32_t kv_full0 = bar + 8, kv_empty0 = kv_full0 + 8 * C::STAGES;
-    const uint32_t s_full0 = kv_empty0 + 8 * C::STAGES, s_empty0 = s_full0 + 16;
-    const uint32_t p_full = s_empty0 + 16, p_empty = p_full + 8;     // one P buffer: phase j belongs to page j
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + (p_empty + 8 - base));
+    const uint32_t k_full0 = bar + 8, k_empty0 = k_full0 + 8 * C::NK;
+    const uint32_t v_full0 = k_empty0 + 8 * C::NK, v_empty0 = v_full0 + 8 * C::NV;
+    const uint32_t s_full0 = v_empty0 + 8 * C::NV;                   // [tile]: the scores of a step are there
+    const uint32_t p_full0 = s_full0 + 8 * FM_TILES;                 // [tile]: the probabilities are written
+    const uint32_t o_full0 = p_full0 + 8 * FM_TILES;                 // [tile]: the last P V is complete
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + (o_full0 + 8 * FM_TILES - base));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, h = blockIdx.y;
     const int tok_begin = a.cu_seqlens[b], n_new = a.cu_seqlens[b + 1] - tok_begin;
     // the last query tiles see the most keys: give them the lowest block indices
-    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * FM_BQ;
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * FM_ROWS;
     if (q0 >= n_new) return;
     const int past = a.past_lens[b];
     const int kvh = h / (a.n_heads / a.n_kv);
     const int* bt = a.block_table + (long)b * a.bt_stride;
-    const int rows_here = min(FM_BQ, n_new - q0);
-    const int pos_first = past + q0, pos_last = past + q0 + rows_here - 1;
-    const int start_first = (a.window > 0 && pos_first - a.window + 1 > 0) ? pos_first - a.window + 1 : 0;
-    const int page_lo = start_first / FM_PAGE, page_hi = pos_last / FM_PAGE + 1;
+    // The two tiles: their rows, the positions they span and the pages those see.  Tile 0 always has rows;
+    // tile 1 has none when the sequence ends inside tile 0.
+    int rows_t[FM_TILES], pos_last_t[FM_TILES], step_lo[FM_TILES], step_hi[FM_TILES];
+    int page_lo = 0, page_hi = 0;
+#pragma unroll
+    for (int t = 0; t < FM_TILES; ++t) {
+        rows_t[t] = max(0, min(FM_BQ, n_new - q0 - t * FM_BQ));
+        const int pf = past + q0 + t * FM_BQ;
+        pos_last_t[t] = pf + max(rows_t[t], 1) - 1;
+        const int sf = (a.window > 0 && pf - a.window + 1 > 0) ? pf - a.window + 1 : 0;
+        const int plo = sf / FM_PAGE, phi = pos_last_t[t] / FM_PAGE + 1;
+        if (t == 0) { page_lo = plo; page_hi = phi; }
+        else if (rows_t[t] > 0) page_hi = phi;
+        step_lo[t] = (plo - page_lo) / FM_NP;
+        step_hi[t] = rows_t[t] > 0 ? (phi - page_lo + FM_NP - 1) / FM_NP : 0;
+        if (rows_t[t] == 0) step_lo[t] = 0;
+    }
     const int n_pages = page_hi - page_lo;
-    const int n_blocks = (n_pages + FM_NP - 1) / FM_NP;           // steps of two pages; the last may hold one
+    const int n_steps = (n_pages + FM_NP - 1) / FM_NP;            // steps of two pages; the last may hold one
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_q);
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
         mbar_init(q_full, 1);
-        for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(kv_full0 + 8 * s, 1);
-            mbar_init(kv_empty0 + 8 * s, 1);
+        for (int s = 0; s < C::NK; ++s) { mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1); }
+        for (int s = 0; s < C::NV; ++s) { mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1); }
+        for (int t = 0; t < FM_TILES; ++t) {
+            mbar_init(s_full0 + 8 * t, 1);
+            mbar_init(p_full0 + 8 * t, 4);       // one arrival per softmax warp of the tile
+            mbar_init(o_full0 + 8 * t, 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(s_full0 + 8 * i, 1);
-            mbar_init(s_empty0 + 8 * i, 4);      // one arrival per softmax warp
-        }
-        mbar_init(p_full, 4);
-        mbar_init(p_empty, 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -140,39 +157,57 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_expect_tx(q_full, C::Q_BYTES);
+            // rows beyond the sequence's tokens are read all the same (another sequence's, or zeros past the
+            // end of the matrix): they compute like real rows and are never stored
+            mbar_expect_tx(q_full, FM_TILES * C::Q_BYTES);
 #pragma unroll
-            for (int x = 0; x < HD / 64; ++x)
-                tma_load_2d(q_smem + x * (FM_BQ * 128), &tmap_q, q_full, h * HD + x * 64, tok_begin + q0);
+            for (int t = 0; t < FM_TILES; ++t)
+#pragma unroll
+                for (int x = 0; x < HD / 64; ++x)
+                    tma_load_2d(q_smem + t * C::Q_BYTES + x * (FM_BQ * 128), &tmap_q, q_full, h * HD + x * 64,
+                                tok_begin + q0 + t * FM_BQ);
             int issued = 0;
-            for (int j = 0; j < n_blocks; ++j, ++issued) {
-                const int s = j % C::STAGES;
-                if (!mbar_wait(kv_empty0 + 8 * s, ((j / C::STAGES) & 1) ^ 1u, abort_flag, a.err, ERR_FM_EMPTY)) break;
+            bool alive = true;
+            for (int j = 0; j < n_steps && alive; ++j, ++issued) {
                 const int np = min(FM_NP, n_pages - j * FM_NP);
-                mbar_expect_tx(kv_full0 + 8 * s, np * 2 * C::PAGE_BYTES);
-                for (int pg = 0; pg < np; ++pg) {
-                    const int row = (bt[page_lo + j * FM_NP + pg] * a.n_kv + kvh) * FM_PAGE;
+                int rows[FM_NP];
+                for (int pg = 0; pg < np; ++pg) rows[pg] = (bt[page_lo + j * FM_NP + pg] * a.n_kv + kvh) * FM_PAGE;
+                // keys: per 64-dim chunk the pages lie one after the other, so the step's keys are rows 0..127 of
+                // one K-major tile; values: page after page, each an MN-major tile of its own
+                const int sk = j % C::NK;
+                if (!mbar_wait(k_empty0 + 8 * sk, ((j / C::NK) & 1) ^ 1u, abort_flag, a.err, ERR_FM_EMPTY)) break;
+                mbar_expect_tx(k_full0 + 8 * sk, np * C::PAGE_BYTES);
+                for (int pg = 0; pg < np; ++pg)
 #pragma unroll
-                    for (int x = 0; x < HD / 64; ++x) {
-                        // keys: per 64-dim chunk the pages lie one after the other, so the step's keys are rows
-                        // 0..127 of one K-major tile; values: page after page, each an MN-major tile of its own
-                        tma_load_2d(k_smem + s * C::KV_BYTES + (x * FM_NP + pg) * (FM_PAGE * 128), &tmap_k,
-                                    kv_full0 + 8 * s, x * 64, row);
-                        tma_load_2d(v_smem + s * C::KV_BYTES + pg * C::PAGE_BYTES + x * (FM_PAGE * 128), &tmap_v,
-                                    kv_full0 + 8 * s, x * 64, row);
-                    }
+                    for (int x = 0; x < HD / 64; ++x)
+                        tma_load_2d(k_smem + sk * C::KV_BYTES + (x * FM_NP + pg) * (FM_PAGE * 128), &tmap_k,
+                                    k_full0 + 8 * sk, x * 64, rows[pg]);
+                const int sv = j % C::NV;
+                if (!mbar_wait(v_empty0 + 8 * sv, ((j / C::NV) & 1) ^ 1u, abort_flag, a.err, ERR_FM_EMPTY)) {
+                    alive = false;
+                    ++issued;                         // the keys of this step are in flight
+                    break;
                 }
+                mbar_expect_tx(v_full0 + 8 * sv, np * C::PAGE_BYTES);
+                for (int pg = 0; pg < np; ++pg)
+#pragma unroll
+                    for (int x = 0; x < HD / 64; ++x)
+                        tma_load_2d(v_smem + sv * C::KV_BYTES + pg * C::PAGE_BYTES + x * (FM_PAGE * 128), &tmap_v,
+                                    v_full0 + 8 * sv, x * 64, rows[pg]);
             }
             if (*abort_flag) {
                 // let copies in flight land before the block gives up its shared memory
                 for (uint32_t i = 0; i < WAIT_POLLS; ++i)
                     if (mbar_try_wait(q_full, 0)) break;
-                const int first = issued > C::STAGES ? issued - C::STAGES : 0;
-                for (int j = first; j < issued; ++j) {
-                    bool landed = false;
-                    for (uint32_t i = 0; i < WAIT_POLLS && !landed; ++i)
-                        landed = mbar_try_wait(kv_full0 + 8 * (j % C::STAGES), (j / C::STAGES) & 1);
-                    if (!landed && a.err) atomicCAS(a.err, 0, ERR_WAIT_DRAIN);
+                for (int ring = 0; ring < 2; ++ring) {
+                    const int n = ring == 0 ? C::NK : C::NV;
+                    const uint32_t full0 = ring == 0 ? k_full0 : v_full0;
+                    const int first = issued > n ? issued - n : 0;
+                    for (int j = first; j < issued; ++j) {
+                        bool landed = false;
+                        for (uint32_t i = 0; i < WAIT_POLLS && !landed; ++i)
+                            landed = mbar_try_wait(full0 + 8 * (j % n), (j / n) & 1);
+                    }
                 }
             }
         }
@@ -183,98 +218,111 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             constexpr uint32_t idesc_s2 = idesc_bf16(FM_BQ, FM_KEYS);         // S: 128 x 128 keys, K = head_dim
             constexpr uint32_t idesc_s1 = idesc_bf16(FM_BQ, FM_PAGE);         // a last step of one page
             constexpr uint32_t idesc_o = idesc_bf16_b_mn(FM_BQ, HD);          // O: 128 x head_dim, K = 16 keys
-            const uint32_t tmem_o = tmem_base;
             bool alive = mbar_wait(q_full, 0, abort_flag, a.err, ERR_FM_Q);
-            for (int j = 0; j <= n_blocks && alive; ++j) {
-                if (j < n_blocks) {
-                    // scores of page j into S buffer j & 1
-                    const int s = j % C::STAGES, sb = j & 1;
-                    if (!mbar_wait(kv_full0 + 8 * s, (j / C::STAGES) & 1, abort_flag, a.err, ERR_FM_KV)) break;
-                    if (!mbar_wait(s_empty0 + 8 * sb, ((j >> 1) & 1) ^ 1u, abort_flag, a.err, ERR_FM_S)) break;
-                    tc_fence_after_sync();
-                    const uint32_t tmem_s = tmem_base + C::S_COL + sb * FM_KEYS;
-                    const uint32_t idesc_s = n_pages - j * FM_NP >= FM_NP ? idesc_s2 : idesc_s1;
+            // step j: for each tile first P V of step j - 1, then the scores of step j
+            for (int j = 0; j <= n_steps && alive; ++j) {
 #pragma unroll
-                    for (int ks = 0; ks < HD / 16; ++ks) {
-                        const uint64_t da = smem_desc_sw128(q_smem + (ks >> 2) * (FM_BQ * 128) + (ks & 3) * 32);
-                        const uint64_t db = smem_desc_sw128(k_smem + s * C::KV_BYTES + (ks >> 2) * (FM_KEYS * 128) + (ks & 3) * 32);
-                        umma_bf16(tmem_s, da, db, idesc_s, ks != 0 ? 1u : 0u);
-                    }
-                    umma_commit(s_full0 + 8 * sb);
-                }
-                if (j >= 1) {
-                    // O += P V for page j - 1, once the softmax has written P
-                    const int jj = j - 1, s = jj % C::STAGES;
-                    if (!mbar_wait(p_full, jj & 1, abort_flag, a.err, ERR_FM_P)) break;
-                    tc_fence_after_sync();
-                    const int np = min(FM_NP, n_pages - jj * FM_NP);
-                    for (int pg = 0; pg < np; ++pg) {
-#pragma unroll
-                        for (int ks = 0; ks < FM_PAGE / 16; ++ks) {
-                            const uint64_t da = smem_desc_sw128(p_smem + pg * (FM_BQ * 128) + ks * 32);
-                            const uint64_t db = smem_desc_sw128_mn(v_smem + s * C::KV_BYTES + pg * C::PAGE_BYTES + ks * 2048,
-                                                                   FM_PAGE * 128);
-                            umma_bf16(tmem_o, da, db, idesc_o, (jj | pg | ks) != 0 ? 1u : 0u);
+                for (int t = 0; t < FM_TILES; ++t) {
+                    if (!alive) break;
+                    const int jj = j - 1;
+                    if (jj >= step_lo[t] && jj < step_hi[t]) {
+                        const int sv = jj % C::NV, lt = jj - step_lo[t];
+                        if (!mbar_wait(v_full0 + 8 * sv, (jj / C::NV) & 1, abort_flag, a.err, ERR_FM_KV) ||
+                            !mbar_wait(p_full0 + 8 * t, lt & 1, abort_flag, a.err, ERR_FM_P)) {
+                            alive = false;
+                            break;
                         }
+                        tc_fence_after_sync();
+                        const int np = min(FM_NP, n_pages - jj * FM_NP);
+                        const uint32_t tmem_o = tmem_base + C::O_COL + t * HD;
+                        const uint32_t tmem_p = tmem_base + C::S_COL + t * FM_KEYS;
+                        for (int pg = 0; pg < np; ++pg) {
+#pragma unroll
+                            for (int ks = 0; ks < FM_PAGE / 16; ++ks) {
+                                const uint64_t db = smem_desc_sw128_mn(
+                                    v_smem + sv * C::KV_BYTES + pg * C::PAGE_BYTES + ks * 2048, FM_PAGE * 128);
+                                umma_bf16_ts(tmem_o, tmem_p + pg * (FM_PAGE / 2) + ks * 8, db, idesc_o,
+                                             (lt | pg | ks) != 0 ? 1u : 0u);
+                            }
+                        }
+                        if (jj == step_hi[t] - 1) umma_commit(o_full0 + 8 * t);
                     }
-                    umma_commit(kv_empty0 + 8 * s);      // the page's stage is free
-                    umma_commit(p_empty);                // so is the P buffer, and O holds pages 0..jj
+                    if (j >= step_lo[t] && j < step_hi[t]) {
+                        const int sk = j % C::NK;
+                        if (!mbar_wait(k_full0 + 8 * sk, (j / C::NK) & 1, abort_flag, a.err, ERR_FM_KV)) {
+                            alive = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t tmem_s = tmem_base + C::S_COL + t * FM_KEYS;
+                        const uint32_t idesc_s = n_pages - j * FM_NP >= FM_NP ? idesc_s2 : idesc_s1;
+#pragma unroll
+                        for (int ks = 0; ks < HD / 16; ++ks) {
+                            const uint64_t da = smem_desc_sw128(q_smem + t * C::Q_BYTES + (ks >> 2) * (FM_BQ * 128) + (ks & 3) * 32);
+                            const uint64_t db = smem_desc_sw128(k_smem + sk * C::KV_BYTES + (ks >> 2) * (FM_KEYS * 128) + (ks & 3) * 32);
+                            umma_bf16(tmem_s, da, db, idesc_s, ks != 0 ? 1u : 0u);
+                        }
+                        umma_commit(s_full0 + 8 * t);
+                    }
                 }
+                if (!alive) break;
+                // both tiles have issued what they read of these stages
+                if (j >= 1) umma_commit(v_empty0 + 8 * ((j - 1) % C::NV));
+                if (j < n_steps) umma_commit(k_empty0 + 8 * (j % C::NK));
             }
         }
         __syncwarp();
     } else {
         // ---------------------------------------------------------------- softmax
-        const int q = warp & 3;
-        const int r = q * 32 + lane;                                  // query row of this thread
+        const int t = (warp - 2) >> 2;                                // tile of this warp
+        const int q = warp & 3;                                       // TMEM lane quarter this warp may touch
+        const int r = q * 32 + lane;                                  // query row of this thread within the tile
         const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-        const bool real = q0 + r < n_new;
+        const uint32_t t_s = t_lane + C::S_COL + t * FM_KEYS;
+        const uint32_t t_o = t_lane + C::O_COL + t * HD;
+        const bool real = r < rows_t[t];
         // rows beyond the sequence's tokens compute like its last row and are never stored
-        const int pos = real ? past + q0 + r : pos_last;
+        const int pos = real ? past + q0 + t * FM_BQ + r : pos_last_t[t];
         const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+        const float scale = a.scale_log2;
+        const float neg_big = -3.0e38f;                               // stands for a masked score before scaling
         float m = -INFINITY, l = 0.f;
         bool alive = true;
-        for (int j = 0; j < n_blocks; ++j) {
-            const int sb = j & 1;
-            alive = warp_mbar_wait(s_full0 + 8 * sb, (j >> 1) & 1, abort_flag, a.err, ERR_FM_S, lane);
+        for (int j = step_lo[t]; j < step_hi[t]; ++j) {
+            const int lt = j - step_lo[t];
+            alive = warp_mbar_wait(s_full0 + 8 * t, lt & 1, abort_flag, a.err, ERR_FM_S, lane);
             if (!alive) break;
             tc_fence_after_sync();
             const int np = min(FM_NP, n_pages - j * FM_NP);
-            float sc[FM_KEYS];
-#pragma unroll
-            for (int c = 0; c < FM_KEYS / 32; ++c) {
-                if (c * 32 < np * FM_PAGE) {
-                    uint32_t v[32];
-                    tmem_ld32(t_lane + C::S_COL + sb * FM_KEYS + c * 32, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) sc[c * 32 + i] = __uint_as_float(v[i]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) sc[c * 32 + i] = 0.f;     // a page that is not there: masked below
-                }
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty0 + 8 * sb);             // this S buffer may be overwritten
             const int key0 = (page_lo + j * FM_NP) * FM_PAGE;
             const int key_end = key0 + np * FM_PAGE - 1;               // last key this step really holds
-            const bool full = np == FM_NP && key0 >= start && key_end <= pos;
-            float mx = -INFINITY;
-            if (full) {
+            const bool full = key0 >= start && key_end <= pos;
+            const int lo_vis = max(start, key0) - key0, hi_vis = min(pos, key_end) - key0;   // visible keys [lo, hi]
+            // first reading: the row's maximum (eight independent chains, so that one warp alone keeps its
+            // pipe busy)
+            float mx8[8];
 #pragma unroll
-                for (int i = 0; i < FM_KEYS; ++i) {
-                    sc[i] *= a.scale_log2;
-                    mx = fmaxf(mx, sc[i]);
-                }
-            } else {
+            for (int i = 0; i < 8; ++i) mx8[i] = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < np * (FM_PAGE / 32); ++c) {
+                uint32_t v[32];
+                tmem_ld32(t_s + c * 32, v);
+                tmem_ld_wait();
+                if (full) {
 #pragma unroll
-                for (int i = 0; i < FM_KEYS; ++i) {
-                    const int key = key0 + i;
-                    sc[i] = (key <= pos && key >= start && key <= key_end) ? sc[i] * a.scale_log2 : -INFINITY;
-                    mx = fmaxf(mx, sc[i]);
+                    for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(v[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int k = c * 32 + i;
+                        const float x = (k >= lo_vis && k <= hi_vis) ? __uint_as_float(v[i]) : neg_big;
+                        mx8[i & 7] = fmaxf(mx8[i & 7], x);
+                    }
                 }
             }
+            float mx_raw = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                                 fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+            const float mx = mx_raw == neg_big ? -INFINITY : mx_raw * scale;       // the scale is positive
             // the reference maximum moves only when the true one has grown by more than 8 (in base 2)
             float corr = 1.0f;
             if (mx > m + 8.0f) {
@@ -282,68 +330,68 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 m = mx;
             }
             const float use = m == -INFINITY ? 0.f : m;
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < FM_KEYS; ++i) {
-                float p;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(sc[i] - use));
-                sc[i] = p;
-                sum += p;
-            }
-            l = l * corr + sum;
-            // Page j-1 must be in O, and its probabilities read, before O is rescaled or P overwritten.
-            // The softmax waited for page j-2 one step ago, so the parity of this phase is unambiguous.
-            if (j > 0) {
-                alive = warp_mbar_wait(p_empty, (j - 1) & 1, abort_flag, a.err, ERR_FM_O, lane);
-                if (!alive) break;
-                tc_fence_after_sync();
-            }
-            // rescale O when some row of the warp moved its reference (never for the first page: O is empty)
-            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+            // rescale O when some row of the warp moved its reference (never in the first step: O is empty)
+            if (lt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
                     uint32_t v[32];
-                    tmem_ld32(t_lane + c * 32, v);
+                    tmem_ld32(t_o + c * 32, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                    tmem_st32(t_lane + c * 32, v);
+                    tmem_st32(t_o + c * 32, v);
                 }
-                tmem_st_wait();
-                tc_fence_before_sync();
             }
-            // P as the A operand of the next product: per page a tile of 128 rows x 64 keys (128 bytes a
-            // row, 8 chunks, swizzled)
-            uint8_t* prow = smem + (p_smem - base) + r * 128;
+            // second reading: exponentials, their sum, and P as bf16 over the first half of the S columns
+            // (chunk c of 32 scores becomes 16 columns at 16 c, always behind the scores still to be read)
+            float sum8[8];
 #pragma unroll
-            for (int c = 0; c < FM_KEYS / 8; ++c) {
-                if (c * 8 >= np * FM_PAGE) break;
-                uint4 pk;
-                __nv_bfloat162 t0 = __floats2bfloat162_rn(sc[c * 8 + 0], sc[c * 8 + 1]);
-                __nv_bfloat162 t1 = __floats2bfloat162_rn(sc[c * 8 + 2], sc[c * 8 + 3]);
-                __nv_bfloat162 t2 = __floats2bfloat162_rn(sc[c * 8 + 4], sc[c * 8 + 5]);
-                __nv_bfloat162 t3 = __floats2bfloat162_rn(sc[c * 8 + 6], sc[c * 8 + 7]);
-                pk.x = *reinterpret_cast<uint32_t*>(&t0); pk.y = *reinterpret_cast<uint32_t*>(&t1);
-                pk.z = *reinterpret_cast<uint32_t*>(&t2); pk.w = *reinterpret_cast<uint32_t*>(&t3);
-                *reinterpret_cast<uint4*>(prow + (c >> 3) * (FM_BQ * 128) + (((c & 7) ^ (r & 7)) << 4)) = pk;
+            for (int i = 0; i < 8; ++i) sum8[i] = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < np * (FM_PAGE / 32); ++c) {
+                uint32_t v[32];
+                tmem_ld32(t_s + c * 32, v);
+                tmem_ld_wait();
+                float x[32];
+                // stage by stage over the 32 scores: neighbouring instructions never depend on one another
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x[i] = fmaf(__uint_as_float(v[i]), scale, -use);
+                if (!full) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int k = c * 32 + i;
+                        if (k < lo_vis || k > hi_vis) x[i] = -INFINITY;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(x[i]) : "f"(x[i]));
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sum8[i & 7] += x[i];
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    __nv_bfloat162 pp = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+                    pk[i] = *reinterpret_cast<uint32_t*>(&pp);
+                }
+                tmem_st16(t_s + c * 16, pk);
             }
-            fence_proxy_async();                                       // visible to the tensor core's reads
+            l = l * corr + (((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7])));
+            tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(p_full0 + 8 * t);
         }
-        // O holds every page: normalise and store this thread's row
-        if (alive) {
-            alive = warp_mbar_wait(p_empty, (n_blocks - 1) & 1, abort_flag, a.err, ERR_FM_O, lane);
-        }
-        if (alive) {
+        // O holds every step: normalise and store this thread's row
+        if (alive && step_hi[t] > step_lo[t])
+            alive = warp_mbar_wait(o_full0 + 8 * t, 0, abort_flag, a.err, ERR_FM_O, lane);
+        if (alive && step_hi[t] > step_lo[t]) {
             tc_fence_after_sync();
             const float inv = 1.0f / l;
-            __nv_bfloat16* orow = a.out + ((long)(tok_begin + q0 + r) * a.n_heads + h) * HD;
+            __nv_bfloat16* orow = a.out + ((long)(tok_begin + q0 + t * FM_BQ + r) * a.n_heads + h) * HD;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(t_lane + c * 32, v);
+                tmem_ld32(t_o + c * 32, v);
                 tmem_ld_wait();
                 if (real) {
 #pragma unroll
@@ -468,10 +516,11 @@ ZLM_EXPORT int zlm_attention_prefill_fmha(const void* q, long q_row_stride, long
     if (B <= 0 || max_new <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size != FM_PAGE || total_tokens <= 0) return ZLM_ERR_BAD_ARG;
     if (hd != 64 && hd != 128) return ZLM_ERR_UNSUPPORTED;
+    if (!(scale > 0.f)) return ZLM_ERR_UNSUPPORTED;            // the row maximum is taken before scaling
     if (((uintptr_t)q % 16) || (q_row_stride % 8) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) ||
         ((uintptr_t)out % 16))
         return ZLM_ERR_UNSUPPORTED;
-    dim3 grid((max_new + FM_BQ - 1) / FM_BQ, n_heads, B);
+    dim3 grid((max_new + FM_ROWS - 1) / FM_ROWS, n_heads, B);
     if (grid.y > 65535 || grid.z > 65535) return ZLM_ERR_UNSUPPORTED;
     CUtensorMap mq, mk, mv;
     int rc = fm_map(&mq, q, total_tokens, (long)n_heads * hd, q_row_stride, FM_BQ);
