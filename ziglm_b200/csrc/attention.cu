@@ -107,6 +107,83 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, long row_stride, int n_he
     }
 }
 
+// The same for bf16 rows whose heads, halves and strides are multiples of 8 elements: a thread moves
+// 16 bytes at a time (8 pairs of the rotation, or 8 elements of a copy), which is what a prompt of
+// thousands of tokens needs to run at memory speed.  Same arithmetic, element by element.
+__global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd,
+                                      int rot, const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                      const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                      int bt_stride, __nv_bfloat16* __restrict__ k_pages,
+                                      __nv_bfloat16* __restrict__ v_pages, int page_size, long page_stride) {
+    __shared__ float cos_s[ROPE_MAX_HALF], sin_s[ROPE_MAX_HALF];
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = positions[t];                       // positions, tables and frequencies are older than the step
+    const int half = rot / 2;
+    const bool have_table = inv_freq != nullptr && half > 0;
+    if (have_table)
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sin_s[i], &cos_s[i]);
+    __nv_bfloat16* kdst = nullptr;
+    __nv_bfloat16* vdst = nullptr;
+    if (k_pages != nullptr && n_kv > 0) {
+        const int b = seq_of_token[t];
+        const int page = block_table[(long)b * bt_stride + pos / page_size];
+        const long off = (long)page * page_stride + (long)(pos % page_size) * hd;
+        kdst = k_pages + off;
+        vdst = v_pages + off;
+    }
+    __syncthreads();
+    pdl_wait();
+    __nv_bfloat16* row0 = qkv + (long)t * row_stride;
+    const long kv_head_stride = (long)page_size * hd;
+    const int total_heads = n_heads + 2 * n_kv;
+    const int per = (total_heads + gridDim.y - 1) / gridDim.y;
+    const int h_lo = blockIdx.y * per, h_hi = min(total_heads, h_lo + per);
+    const int rot_hi = min(h_hi, n_heads + n_kv);
+    if (have_table && rot_hi > h_lo) {
+        const int units = half / 8;
+        for (int idx = threadIdx.x; idx < (rot_hi - h_lo) * units; idx += blockDim.x) {
+            const int head = h_lo + idx / units, i0 = (idx % units) * 8;
+            __nv_bfloat16* row = row0 + (long)head * hd;
+            uint4 lo = *reinterpret_cast<const uint4*>(row + i0);
+            uint4 hi = *reinterpret_cast<const uint4*>(row + i0 + half);
+            __nv_bfloat162* lp = reinterpret_cast<__nv_bfloat162*>(&lo);
+            __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 x = __bfloat1622float2(lp[k]), y = __bfloat1622float2(hp[k]);
+                const float c0 = cos_s[i0 + 2 * k], s0 = sin_s[i0 + 2 * k];
+                const float c1 = cos_s[i0 + 2 * k + 1], s1 = sin_s[i0 + 2 * k + 1];
+                lp[k] = __halves2bfloat162(__float2bfloat16_rn(x.x * c0 - y.x * s0), __float2bfloat16_rn(x.y * c1 - y.y * s1));
+                hp[k] = __halves2bfloat162(__float2bfloat16_rn(x.x * s0 + y.x * c0), __float2bfloat16_rn(x.y * s1 + y.y * c1));
+            }
+            *reinterpret_cast<uint4*>(row + i0) = lo;
+            *reinterpret_cast<uint4*>(row + i0 + half) = hi;
+            if (kdst && head >= n_heads) {
+                __nv_bfloat16* d = kdst + (long)(head - n_heads) * kv_head_stride;
+                *reinterpret_cast<uint4*>(d + i0) = lo;
+                *reinterpret_cast<uint4*>(d + i0 + half) = hi;
+            }
+        }
+    }
+    if (kdst) {
+        const int k_first = have_table ? rot : 0;
+        const int k_units = (hd - k_first) / 8;
+        const int k_lo = max(h_lo, n_heads), k_hi = rot_hi;
+        for (int idx = threadIdx.x; idx < (k_hi - k_lo) * k_units; idx += blockDim.x) {
+            const int h = k_lo - n_heads + idx / k_units, i = k_first + (idx % k_units) * 8;
+            *reinterpret_cast<uint4*>(kdst + (long)h * kv_head_stride + i) =
+                *reinterpret_cast<const uint4*>(row0 + (long)(n_heads + h) * hd + i);
+        }
+        const int v_lo = max(h_lo, n_heads + n_kv), v_units = hd / 8;
+        for (int idx = threadIdx.x; idx < (h_hi - v_lo) * v_units; idx += blockDim.x) {
+            const int h = v_lo - n_heads - n_kv + idx / v_units, i = (idx % v_units) * 8;
+            *reinterpret_cast<uint4*>(vdst + (long)h * kv_head_stride + i) =
+                *reinterpret_cast<const uint4*>(row0 + (long)(n_heads + n_kv + h) * hd + i);
+        }
+    }
+}
+
 // ------------------------------------------------------------ attention
 // grid (T, n_heads); 128 threads.  Warp w takes the key blocks w, w+4, ... of 32
 // keys; lane j scores key j of the block, then the lanes split the head's
@@ -264,6 +341,11 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
         e = launch_pdl(rope_store_kernel<float>, grid, dim3(threads), 0, stream, (float*)qkv, row_stride, n_heads, n_kv,
                        hd, rot, inv_freq, positions, seq_of_token, block_table, bt_stride, (float*)k_pages,
                        (float*)v_pages, page_size, page_stride);
+    else if (dtype == ZLM_BF16 && hd % 8 == 0 && rot % 16 == 0 && row_stride % 8 == 0 && page_stride % 8 == 0 &&
+             (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0)
+        e = launch_pdl(rope_store_vec_kernel, grid, dim3(work >= 256 * 8 ? 256 : (work >= 128 * 8 ? 128 : 64)), 0, stream,
+                       (__nv_bfloat16*)qkv, row_stride, n_heads, n_kv, hd, rot, inv_freq, positions, seq_of_token,
+                       block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, page_stride);
     else if (dtype == ZLM_BF16)
         e = launch_pdl(rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)qkv,
                        row_stride, n_heads, n_kv, hd, rot, inv_freq, positions, seq_of_token, block_table, bt_stride,
