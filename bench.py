@@ -335,6 +335,116 @@ def run_case(args):
     return 0
 
 
+REFERENCE_LIB = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "libziglm_cuda.so")
+
+
+def run_reference_kernels(args):
+    """The reference's own CUDA kernels (its src/cuda_bridge.cu, unmodified, compiled for sm_100a into
+    baseline/_ref/libziglm_cuda.so), timed at the shapes of this benchmark and put together in the order its
+    decode step calls them for one Llama layer (src/model.zig:600-760): one sequence, float32 activations and
+    cache, bf16 weights.  This is not the reference arm (its engine is a Zig program): it says what the
+    reference's kernels alone would give on this GPU."""
+    import ctypes
+    from ctypes import c_float, c_int, c_void_p
+    import torch
+    if not os.path.isfile(REFERENCE_LIB):
+        print(json.dumps({"case": "reference-kernels", "unavailable":
+                          "baseline/_ref/libziglm_cuda.so is not there (build it from the reference's "
+                          "src/cuda_bridge.cu with nvcc -shared -gencode arch=compute_100a,code=sm_100a)"}))
+        return 0
+    lib = ctypes.CDLL(REFERENCE_LIB)
+    P = c_void_p
+    protos = {
+        "cuda_gemv_bf16": [P, P, P, c_int, c_int, P],
+        "cuda_rmsnorm": [P, P, P, c_int, c_float, c_int, P],
+        "cuda_rope": [P, P, c_int, c_int, c_int, c_int, c_int, c_float, P],
+        "cuda_kv_cache_put": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
+        "cuda_attention_forward": [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, P],
+        "cuda_swiglu": [P, P, P, c_int, P],
+        "cuda_add": [P, P, c_int, P],
+    }
+    for name, argtypes in protos.items():
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = argtypes, None
+    torch.cuda.set_device(0)
+    dev = "cuda:0"
+    c = LLAMA_8B
+    H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+    nh, nkv, hd = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+    ctx = args.context
+    stream = torch.cuda.current_stream().cuda_stream
+    bf = lambda r, k: (torch.randn(r, k, device=dev) * 0.02).to(torch.bfloat16)
+    f32 = lambda n: torch.randn(n, device=dev)
+    w = {"q": bf(nh * hd, H), "k": bf(nkv * hd, H), "v": bf(nkv * hd, H), "o": bf(H, nh * hd), "gate": bf(I, H),
+         "up": bf(I, H), "down": bf(H, I), "head": bf(V, H)}
+    g1, g2 = torch.ones(H, device=dev), torch.ones(H, device=dev)
+    x, h, q, k, v, att, o = f32(H), f32(H), f32(nh * hd), f32(nkv * hd), f32(nkv * hd), f32(nh * hd), f32(H)
+    gate, up, act, down, logits = f32(I), f32(I), f32(I), f32(H), f32(V)
+    kc = torch.randn(ctx, nkv * hd, device=dev)
+    vc = torch.randn(ctx, nkv * hd, device=dev)
+    pos, eps, scale = ctx - 1, c["rms_norm_eps"], 1.0 / hd ** 0.5
+    p = lambda t: t.data_ptr()
+    steps = {
+        "rmsnorm": lambda: lib.cuda_rmsnorm(p(x), p(g1), p(h), H, eps, 0, stream),
+        "gemv_q": lambda: lib.cuda_gemv_bf16(p(w["q"]), p(h), p(q), nh * hd, H, stream),
+        "gemv_k": lambda: lib.cuda_gemv_bf16(p(w["k"]), p(h), p(k), nkv * hd, H, stream),
+        "gemv_v": lambda: lib.cuda_gemv_bf16(p(w["v"]), p(h), p(v), nkv * hd, H, stream),
+        "rope": lambda: lib.cuda_rope(p(q), p(k), pos, nh, nkv, hd, hd, c["rope_theta"], stream),
+        "kv_put": lambda: lib.cuda_kv_cache_put(p(kc), p(vc), p(k), p(v), 0, pos, ctx, nkv, hd, nkv * hd, stream),
+        "attention": lambda: lib.cuda_attention_forward(p(q), p(kc), p(vc), p(att), 0, pos, ctx, nh, nkv, hd, nkv * hd,
+                                                        scale, 0.0, 0, stream),
+        "gemv_o": lambda: lib.cuda_gemv_bf16(p(w["o"]), p(att), p(o), H, nh * hd, stream),
+        "add_1": lambda: lib.cuda_add(p(x), p(o), H, stream),
+        "rmsnorm_2": lambda: lib.cuda_rmsnorm(p(x), p(g2), p(h), H, eps, 0, stream),
+        "gemv_gate": lambda: lib.cuda_gemv_bf16(p(w["gate"]), p(h), p(gate), I, H, stream),
+        "gemv_up": lambda: lib.cuda_gemv_bf16(p(w["up"]), p(h), p(up), I, H, stream),
+        "swiglu": lambda: lib.cuda_swiglu(p(gate), p(up), p(act), I, stream),
+        "gemv_down": lambda: lib.cuda_gemv_bf16(p(w["down"]), p(act), p(down), H, I, stream),
+        "add_2": lambda: lib.cuda_add(p(x), p(down), H, stream),
+    }
+    # The reference's cuda_argmax is left out: it hands its kernels the host-side names of two __device__
+    # arrays as pointers (src/cuda_bridge.cu:2943-2944, 3075-3076), which is an illegal memory access on
+    # this GPU; it ran here once and is not run again.
+    tail = {
+        "gemv_head": lambda: lib.cuda_gemv_bf16(p(w["head"]), p(h), p(logits), V, H, stream),
+    }
+    flush = torch.empty(160 * 1024 * 1024, dtype=torch.uint8, device=dev)       # larger than L2
+
+    def timed(fn, reps):
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1000.0)
+        return sorted(ts)[len(ts) // 2]
+
+    for name, fn in {**steps, **tail}.items():        # one by one first: a failing launch is named
+        fn()
+        try:
+            torch.cuda.synchronize()
+        except RuntimeError as e:
+            print(json.dumps({"case": "reference-kernels", "unavailable": "%s failed: %s" % (name, str(e).splitlines()[0])}))
+            return 0
+    each = {name: round(timed(fn, 7), 1) for name, fn in {**steps, **tail}.items()}
+
+    def layer():
+        for fn in steps.values():
+            fn()
+    layer_us = timed(layer, 7)
+    tail_us = each["rmsnorm"] + each["gemv_head"]
+    token_ms = (layer_us * c["num_hidden_layers"] + tail_us) / 1000.0
+    print(json.dumps({"case": "reference-kernels", "what": "simonproyt/ziglm src/cuda_bridge.cu compiled for sm_100a, one "
+                      "sequence, context %d, Llama-3.1-8B layer shapes; L2 flushed before every timing; without its argmax "
+                      "(faults here)" % ctx,
+                      "kernel_us": each, "layer_us": round(layer_us, 1),
+                      "decode_b1_ms_per_token": round(token_ms, 3), "decode_b1_tok_s": round(1000.0 / token_ms, 1)}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
@@ -343,8 +453,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the configuration has (both numbers are reported)")
-    ap.add_argument("--case", default="full", choices=["full", "prefill", "decode"],
-                    help="full: the whole measurement; prefill / decode: that phase alone (for profilers)")
+    ap.add_argument("--case", default="full", choices=["full", "prefill", "decode", "reference-kernels"],
+                    help="full: the whole measurement; prefill / decode: that phase alone (for profilers); "
+                         "reference-kernels: the reference's CUDA kernels alone, if they were built")
     ap.add_argument("--batch", type=int, default=8, help="--case decode: sequences in the batch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="--case decode: tokens each sequence holds")
     args = ap.parse_args()
@@ -356,6 +467,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this library has no multi-GPU path (asked for --gpus {args.gpus})")
         return 2
+    if args.case == "reference-kernels":
+        return run_reference_kernels(args)
     if args.case != "full":
         return run_case(args)
     return run_ours(args)

@@ -509,15 +509,8 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const CUtenso
     attr[1].val.clusterDim.x = 1;
     attr[1].val.clusterDim.y = 1;
     attr[1].val.clusterDim.z = a.splits;
-    static const bool no_pdl = getenv("ZLM_NO_PDL") != nullptr;
-    if (no_pdl) {
-        attr[0] = attr[1];
-        cfg.attrs = attr;
-        cfg.numAttrs = a.splits > 1 ? 1 : 0;
-    } else {
-        cfg.attrs = attr;
-        cfg.numAttrs = a.splits > 1 ? 2 : 1;
-    }
+    cfg.attrs = attr;
+    cfg.numAttrs = a.splits > 1 ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, MODE>, mw, mx, my, a);
     return e == cudaSuccess ? launch_status() : (int)e;
 }
@@ -595,8 +588,7 @@ ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int b
                                 : (y_dtype == ZLM_BF16 ? OUT_BF16 : (accumulate ? OUT_F32_ACC : OUT_F32));
     // the output goes through TMA when its rows start on 16-byte boundaries; else the threads store directly
     const int es = y_dtype == ZLM_BF16 ? 2 : 4;
-    static const bool no_tma_store = getenv("ZLM_NO_TMA_STORE") != nullptr;
-    a.tma_store = ((uintptr_t)Y % 16 == 0) && ((ldy * es) % 16 == 0) && !no_tma_store;
+    a.tma_store = ((uintptr_t)Y % 16 == 0) && ((ldy * es) % 16 == 0);
     if (a.tma_store) {
         rc = cached_map(&my, Y, T, n_out, ldy, sub_rows(bn), glu ? TC_BM / 2 : TC_BM, es == 2 ? 1 : 2);
         if (rc) return rc;
