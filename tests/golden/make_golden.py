@@ -3,7 +3,8 @@
 The reference's own model code is Zig and cannot be compiled or imported in this
 environment, so these outputs come from tests/plain_llama.py (written from the
 reference's formulas) and pin it against accidental change; they are not outputs
-of the reference.
+of the reference.  The parts of the plain implementation are checked against the
+reference's own CUDA kernels separately (make_reference_kernel_golden.py).
 
     python tests/golden/make_golden.py
 """
