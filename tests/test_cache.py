@@ -128,3 +128,36 @@ def test_random_traffic_keeps_every_slot_and_page_accounted_for():
         t.free(s)
     t.check()
     assert all(g.pool.n_free == g.pool.capacity for g in t.groups) and t.slots.n_free == 5
+
+
+def test_the_array_of_block_tables_follows_the_lists():
+    """The pages of a slot are also kept as a row of an int32 array (what a step copies to the device):
+    after growth, release behind a window, freeing and reuse the two agree."""
+    import numpy as np
+    from ziglm_b200.cache.slots import GroupPages, SlotTable
+    groups = [GroupPages(40, 4, None), GroupPages(40, 4, 6)]
+    for g in groups:
+        g.mirror(5, 10)
+    table = SlotTable(5, groups, 40)
+
+    def check():
+        for g in groups:
+            for slot in range(5):
+                pages = g.pages_of.get(slot, [])
+                want = np.full(10, -1, dtype=np.int32)
+                want[:len(pages)] = pages
+                assert (g.table[slot] == want).all()
+
+    a, b = table.alloc(), table.alloc()
+    for n_a, n_b in ((3, 9), (1, 1), (6, 2), (1, 1), (13, 5)):
+        table.reserve({a: n_a, b: n_b})
+        table.advance({a: n_a, b: n_b})
+        check()
+    assert (groups[1].table[a, :3] == -1).all()        # behind the window of 6 after 24 positions
+    table.free(a)
+    check()
+    c = table.alloc()
+    table.reserve({c: 7})
+    table.advance({c: 7})
+    check()
+    table.check()

@@ -15,6 +15,7 @@ correspond to :class:`CacheFull` and :class:`SequenceTooLong` here.
 from __future__ import annotations
 
 import heapq
+import numpy as np
 from typing import Dict, List, Optional
 
 
@@ -89,6 +90,14 @@ class GroupPages:
         self.page_size = page_size
         self.window = window
         self.pages_of: Dict[int, List[int]] = {}     # slot -> page per block index (-1: released)
+        self.table: Optional[np.ndarray] = None      # the same as rows of an int32 array, once its size is known
+
+    def mirror(self, n_slots: int, max_pages: int) -> None:
+        """Keep the pages of every slot also as row ``slot`` of an int32 array [n_slots, max_pages] (-1: none),
+        so that a step's block table is one indexing operation."""
+        self.table = np.full((n_slots, max_pages), -1, dtype=np.int32)
+        for slot, pages in self.pages_of.items():
+            self.table[slot, :len(pages)] = pages
 
     def pages_needed(self, slot: int, new_len: int) -> int:
         have = len(self.pages_of.get(slot, ()))
@@ -99,6 +108,8 @@ class GroupPages:
         want = -(-new_len // self.page_size)
         while len(pages) < want:
             pages.append(self.pool.take())
+            if self.table is not None and len(pages) <= self.table.shape[1]:
+                self.table[slot, len(pages) - 1] = pages[-1]
 
     def release_behind_window(self, slot: int, length: int) -> None:
         """Give back pages whose every position lies before the window of the next token."""
@@ -110,11 +121,15 @@ class GroupPages:
             if pages[i] >= 0:
                 self.pool.give_back(pages[i])
                 pages[i] = -1
+                if self.table is not None and i < self.table.shape[1]:
+                    self.table[slot, i] = -1
 
     def free(self, slot: int) -> None:
         for p in self.pages_of.pop(slot, []):
             if p >= 0:
                 self.pool.give_back(p)
+        if self.table is not None:
+            self.table[slot, :] = -1
 
 
 class SlotTable:

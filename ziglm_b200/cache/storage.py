@@ -73,6 +73,8 @@ class CacheStorage:
             if src is not None and src not in self.group_of:
                 raise ValueError(f"place {s} of the schedule reads the cache of place {src}, which keeps none")
         self.slots = SlotTable(n_slots, [g.pages for g in self.groups], max_len)
+        for g in self.groups:
+            g.pages.mirror(n_slots, self.max_pages_per_seq)
         self.states: Dict[int, torch.Tensor] = {}
         for s, need in enumerate(state_needs):
             if need is not None:
@@ -89,7 +91,11 @@ class CacheStorage:
         self.slots.free(slot)
 
     # ------------------------------------------------------------- block tables
-    def block_table_rows(self, group: int, slots: Sequence[int], width: int) -> List[List[int]]:
+    def block_table_rows(self, group: int, slots: Sequence[int], width: int):
+        """Pages of the given slots as an int32 array [len(slots), width] (-1 where there is none)."""
+        table = self.groups[group].pages.table
+        if table is not None and width <= table.shape[1]:
+            return table[list(slots), :width]
         pages = self.groups[group].pages.pages_of
         rows = []
         for s in slots:

@@ -17,6 +17,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -75,31 +76,47 @@ class StepContext:
 
 
 def pack_batch(layout: BatchLayout, host: torch.Tensor, slots: Sequence[int], past_lens: Sequence[int],
-               new_tokens: Sequence[Sequence[int]], want_rows: Sequence[int],
-               tables: Sequence[Sequence[Sequence[int]]]) -> None:
-    """Fill the pinned int32 buffer ``host`` according to ``layout``."""
+               new_tokens: Sequence[Sequence[int]], want_rows: Sequence[int], tables: Sequence[Any]) -> None:
+    """Fill the pinned int32 buffer ``host`` according to ``layout``.  ``tables``: per cache group the block
+    table rows of the batch's sequences, a list of lists or an int32 array [B, width]."""
     o = layout.offsets
-    toks: List[int] = []
-    pos: List[int] = []
-    seq: List[int] = []
-    cu = [0]
-    for b, (past, new) in enumerate(zip(past_lens, new_tokens)):
-        toks.extend(new)
-        pos.extend(range(past, past + len(new)))
-        seq.extend([b] * len(new))
-        cu.append(cu[-1] + len(new))
-    total = [p + len(n) for p, n in zip(past_lens, new_tokens)]
+    buf = host.numpy()                       # shares the pinned memory
+    B = len(slots)
 
-    def put(name: str, values: Sequence[int]) -> None:
-        if values:
-            host[o[name]:o[name] + len(values)] = torch.tensor(values, dtype=torch.int32)
+    def put(name: str, values) -> None:
+        n = len(values)
+        if n:
+            buf[o[name]:o[name] + n] = values
 
-    put("tokens", toks); put("positions", pos); put("seq_of_token", seq); put("cu_seqlens", cu)
-    put("past_lens", list(past_lens)); put("total_lens", total); put("slots", list(slots))
-    put("want_rows", list(want_rows))
+    if all(len(t) == 1 for t in new_tokens):
+        # a decode step: one token per sequence, position = length so far
+        put("tokens", [t[0] for t in new_tokens])
+        put("positions", past_lens)
+        put("seq_of_token", _ARANGE[:B] if B <= len(_ARANGE) else np.arange(B, dtype=np.int32))
+        put("cu_seqlens", _ARANGE[:B + 1] if B < len(_ARANGE) else np.arange(B + 1, dtype=np.int32))
+        put("past_lens", past_lens)
+        put("total_lens", [p + 1 for p in past_lens])
+    else:
+        toks: List[int] = []
+        pos: List[int] = []
+        seq: List[int] = []
+        cu = [0]
+        for b, (past, new) in enumerate(zip(past_lens, new_tokens)):
+            toks.extend(new)
+            pos.extend(range(past, past + len(new)))
+            seq.extend([b] * len(new))
+            cu.append(cu[-1] + len(new))
+        put("tokens", toks); put("positions", pos); put("seq_of_token", seq); put("cu_seqlens", cu)
+        put("past_lens", past_lens)
+        put("total_lens", [p + len(n) for p, n in zip(past_lens, new_tokens)])
+    put("slots", slots)
+    put("want_rows", want_rows)
     for g, rows in enumerate(tables):
-        flat = [p for row in rows for p in row]
+        flat = np.asarray(rows, dtype=np.int32).reshape(-1)
         put(f"table{g}", flat)
+
+
+_ARANGE = np.arange(4097, dtype=np.int32)
 
 
 def views(layout: BatchLayout, dev: torch.Tensor) -> Dict[str, Any]:
