@@ -34,8 +34,26 @@ TINY_C = {
     "rope_theta": 10000.0, "max_position_embeddings": 512, "rms_norm_eps": 1e-5,
     "tie_word_embeddings": False, "attention_bias": False,
 }
-NORM_JITTER = {"A": 0.0, "B": 0.1, "C": 0.1}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Two with the head sizes the tensor-core attention kernels take (64 and 128): grouped heads with an even and
+# with an odd group, a feed-forward width that is no multiple of a tile, biases and llama3 scaling in one.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 256, "intermediate_size": 688, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 500,
+    "rope_theta": 10000.0, "max_position_embeddings": 512, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "attention_bias": False,
+}
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 384, "intermediate_size": 512, "num_hidden_layers": 2,
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 128, "vocab_size": 300,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "max_position_embeddings": 512, "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "attention_bias": True,
+}
+NORM_JITTER = {"A": 0.0, "B": 0.1, "C": 0.1, "D": 0.1, "E": 0.1}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_folder(tmp_path, cfg: dict, seed: int, dtype: torch.dtype, norm_jitter: float = 0.0, std: float = 0.02) -> str:

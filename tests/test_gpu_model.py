@@ -11,7 +11,8 @@ pytestmark = pytest.mark.gpu
 
 DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 # request lengths per configuration: a one-token request, lengths around the page size of 64, a long one
-LENGTHS = {"A": [5, 11, 17, 70, 45, 128], "B": [1, 9, 23, 40, 97, 64], "C": [3, 65, 33, 128, 12, 50]}
+LENGTHS = {"A": [5, 11, 17, 70, 45, 128], "B": [1, 9, 23, 40, 97, 64], "C": [3, 65, 33, 128, 12, 50],
+           "D": [5, 130, 64, 200, 17, 96], "E": [1, 129, 70, 33, 250, 16]}
 
 
 class Zoo:
@@ -50,7 +51,10 @@ def zoo(tmp_path_factory):
     return Zoo(tmp_path_factory.mktemp("models"))
 
 
-CASES = [(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")]
+# D and E have the head sizes of the tensor-core attention kernels: in bfloat16 their prompts run the tcgen05
+# kernel (or the mma.sync one below 16 tokens) and their decode steps the flat kernel with rotation and cache write
+CASES = [(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")] + [("D", "bfloat16"), ("E", "bfloat16"),
+                                                                              ("D", "float32")]
 
 
 @pytest.mark.parametrize("name,dn", CASES)
@@ -144,7 +148,8 @@ def test_float32_does_not_depend_on_the_schedule(zoo, name, dn):
         assert (got[r] - whole[r]).abs().max().item() <= 1e-6
 
 
-@pytest.mark.parametrize("name,dn", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16"), ("B", "float32")])
+@pytest.mark.parametrize("name,dn", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16"), ("B", "float32"),
+                                     ("D", "bfloat16"), ("E", "bfloat16")])
 def test_long_decoding(zoo, name, dn):
     _, eng = zoo.get(name, dn)
     V = helpers.CONFIGS[name]["vocab_size"]
@@ -232,3 +237,34 @@ def test_single_sequence_calls_of_the_reference(zoo):
     eng.reset()
     helpers.assert_close(eng.prefill(toks[:2]).clone(), want[1], torch.float32, "after reset")
     eng.reset()
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_tensor_core_head_sizes_take_the_tensor_core_attention(zoo, name, monkeypatch):
+    """With head size 64 or 128 in bfloat16 no step goes through the plain attention kernel, and a decode step
+    needs no separate rotation kernel (the flat kernel rotates and writes the cache itself)."""
+    from ziglm_b200 import kernels
+    _, eng = zoo.get(name, "bfloat16")
+    V = helpers.CONFIGS[name]["vocab_size"]
+
+    def never(*a, **k):
+        raise AssertionError("the plain attention kernel ran")
+    monkeypatch.setattr(kernels, "attention_general", never)
+    slot = eng.alloc_slot()
+    eng.step([(slot, helpers.random_tokens(40, V, 5))])           # tcgen05 prompt kernel
+    eng.step([(slot, helpers.random_tokens(3, V, 6))])            # mma.sync prompt kernel (fewer than 16 tokens)
+
+    def no_rotation(*a, **k):
+        raise AssertionError("a decode step launched the rotation kernel")
+    monkeypatch.setattr(kernels, "rope_store", no_rotation)
+    before = kernels.launches()
+    eng.options.use_graphs = False
+    try:
+        eng.step([(slot, [7])])
+    finally:
+        eng.options.use_graphs = True
+    eng.free_slot(slot)
+    layers = helpers.CONFIGS[name]["num_hidden_layers"]
+    # per layer: norm, q|k|v, attention, o, norm, gate|up with activation, down; then embedding, norm, head
+    assert kernels.launches() - before == 7 * layers + 3
+    assert kernels.attention_tc_status() == 0 and kernels.attention_fmha_status() == 0
