@@ -78,7 +78,7 @@ def test_gemm_tc_rows_of_wider_buffers_and_odd_output_stride(K):
     assert K.gemm_tc(x, w, out) is False
     xb = rnd((20, 304), BF, seed=9).to(DEV)
     x = xb[:, 40:168]
-    assert K.gemm_tc(x, w, out) is True                   # output rows of 50 floats: stored by the threads
+    assert K.gemm_tc(x, w, out) == 1                      # output rows of 50 floats: stored by the threads
     assert torch.allclose(out.cpu(), ref_product(x.cpu(), w.cpu()), atol=1e-3, rtol=1e-3)
     wide = torch.zeros(20, 64, dtype=torch.float32, device=DEV)
     assert K.gemm_tc(x, w, wide[:, :50], accumulate=True)  # output rows inside a wider buffer: through TMA
@@ -296,3 +296,46 @@ def test_tc_attention_refuses_other_head_sizes(K):
     pages = torch.zeros(1, 1, 64, 48, dtype=BF, device=DEV)
     z = torch.zeros(2, dtype=torch.int32, device=DEV)
     assert K.attention_prefill(q, out, 1, 1, 1, 1, 48, 1.0, None, z, z, z.view(1, 2), pages, pages, 64) is False
+
+
+@pytest.mark.parametrize("T", [1, 8, 17, 64])
+@pytest.mark.parametrize("d,k1,n2", [(256, 2048, 640), (4096, 512, 256), (200, 1024, 136), (256, 128, 64)])
+@pytest.mark.parametrize("gain_dtype", [torch.float32, BF])
+def test_gemm_tc_carries_an_rmsnorm_between_two_products(K, T, d, k1, n2, gain_dtype):
+    """residual += a W1^T with the first half of the norm (x * gain as bf16, sums of squares per tile row), then
+    (x * gain) W2^T scaled by 1 / sqrt(mean x^2 + eps) per row, plain and with the gated activation: the same
+    as the residual sum, an RMSNorm kernel and the product."""
+    eps = 1e-5
+    a = rnd((T, k1), BF, 1.0, seed=1).to(DEV)
+    w1 = rnd((d, k1), BF, 0.05, seed=2).to(DEV)
+    x0 = rnd((T, d), torch.float32, 1.0, seed=3).to(DEV)
+    gain = (1.0 + 0.2 * rnd((d,), torch.float32, 1.0, seed=4)).to(gain_dtype).to(DEV)
+    w2 = rnd((n2, d), BF, 0.05, seed=5).to(DEV)
+    bias = rnd((n2,), torch.float32, 1.0, seed=6).to(DEV)
+    x = x0.clone()
+    hb = torch.full((T, d), float("nan"), dtype=BF, device=DEV)
+    ssq = torch.full((T, -(-d // 128)), float("nan"), device=DEV)
+    done = K.gemm_tc(a, w1, x, accumulate=True, norm_out=(gain, 0.0, hb, ssq))
+    x_ref = x0 + a.float() @ w1.float().t()
+    assert torch.allclose(x, x_ref, atol=2e-3, rtol=2e-3)
+    if done != 2:
+        # too few K blocks to split over a cluster: the product says so and leaves hb and ssq alone
+        assert done == 1 and torch.isnan(hb.float()).all() and torch.isnan(ssq).all()
+        return
+    assert torch.allclose(ssq.sum(1), (x * x).sum(1), rtol=1e-5)
+    assert torch.equal(hb, (x * gain.float()).to(BF))
+    h_ref = (x * (1.0 / torch.sqrt((x * x).mean(1, keepdim=True) + eps)) * gain.float()).to(BF)
+    want = h_ref.float() @ w2.float().t() + bias
+    got = torch.zeros(T, n2, device=DEV)
+    assert K.gemm_tc(hb, w2, got, bias=bias, row_scale=(ssq, eps))
+    torch.cuda.synchronize()
+    scale = want.abs().max().item()
+    assert (got - want).abs().max().item() <= 1e-2 * scale
+    # the gated mode: rows of w2 alternate gate and up
+    gu = h_ref.float() @ w2.float().t()
+    want_act = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
+    act = torch.zeros(T, n2 // 2, dtype=BF, device=DEV)
+    assert K.gemm_tc(hb, w2, act, glu="silu", row_scale=(ssq, eps))
+    torch.cuda.synchronize()
+    assert (act.float() - want_act).abs().max().item() <= 2e-2 * max(want_act.abs().max().item(), 1e-3)
+    assert K.gemm_tc_status() == 0

@@ -53,6 +53,19 @@ struct TcArgs {
     int grid_x;          // blocks (clusters when K is split) that share the tiles
     int tma_store;       // the output goes through shared memory and a TMA store / reduce
     int glu_kind;        // gated mode: 0 silu, 1 tanh gelu
+    // RMSNorm split over two products (steps of a few tokens, see zlm_gemm_tc_norm):
+    // this product finishes the residual sum and leaves x * gain as bf16 and the sums of squares per tile row
+    const void* norm_gain;      // [N] gain of the norm that follows, or null
+    int norm_gain_dtype;
+    float norm_offset;          // added to the gain (1 for the architectures that store gain - 1)
+    __nv_bfloat16* norm_hb;     // [T, ld_hb] bf16(x_new * gain)
+    long ld_hb;
+    float* norm_ssq;            // [T, norm_p] sums of x_new^2 over the 128 features of tile row p
+    int norm_p;
+    // this product reads x * gain and scales every output row by 1 / sqrt(mean x^2 + eps)
+    const float* scale_ssq;     // [T, scale_p] or null
+    int scale_p;
+    float scale_eps;
     int* err;
 };
 
@@ -117,6 +130,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
     float* partial = reinterpret_cast<float*>(smem);   // split-K only (one tile per block): [BN][128] floats
 
+    __shared__ float inv_s[64];                     // row scales of a product that completes a norm
+    __shared__ float norm_red[2][4];                // sums of squares of the four warps of an epilogue half
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = a.splits > 1 ? cluster_rank() : 0u;
     const int kb0 = (int)rank * a.kb_per_split;
@@ -231,6 +246,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     } else {
         // ---------------------------------------------------------------- epilogue
         grid_dependency_wait();                     // the output may still be read by the kernel before this one
+        if (a.scale_ssq != nullptr) {
+            // one token tile (the host makes sure): 1 / sqrt(mean x^2 + eps) of its tokens, partial sums in order
+            const int et = (int)threadIdx.x - 64;
+            if (et < BN && et < 64) {
+                float inv = 1.0f;
+                if (et < a.T) {
+                    float ss = 0.f;
+                    for (int p = 0; p < a.scale_p; ++p) ss += a.scale_ssq[(long)et * a.scale_p + p];
+                    inv = 1.0f / sqrtf(ss / (float)a.K + a.scale_eps);
+                }
+                inv_s[et] = inv;
+            }
+        }
         const int q = warp & 3;                     // TMEM lane quarter this warp may read
         const int egroup = (warp - 2) >> 2;         // which of the two warps of that quarter
         const int f_local = q * 32 + lane;
@@ -285,6 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 float val = part[0];
 #pragma unroll
                 for (int r = 1; r < 8; ++r) val += part[r];
+                if (a.scale_ssq != nullptr) val *= inv_s[cc];
                 val += bias_v;
                 if (GLU) {
                     const float up = __shfl_down_sync(0xffffffffu, val, 1);
@@ -294,10 +323,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 if (writer && out_f < out_n) {
                     if (MODE == OUT_BF16 || GLU)
                         reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
-                    else if (MODE == OUT_F32_ACC)       // one adder per element: the order is fixed
+                    else if (MODE == OUT_F32_ACC && a.norm_gain == nullptr)   // one adder per element: the order is fixed
                         atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
-                    else
+                    else if (MODE != OUT_F32_ACC)
                         reinterpret_cast<float*>(a.Y)[(long)tok * a.ldy + out_f] = val;
+                }
+                if (MODE == OUT_F32_ACC && a.norm_gain != nullptr) {
+                    // The only adder of this element sees the finished residual value: it leaves x * gain for
+                    // the product after the norm, and the tile's 128 features of this token give one partial
+                    // sum of squares (four warps of this half of the epilogue, summed in warp order).
+                    float xn = 0.f;
+                    if (out_f < out_n) {
+                        xn = atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val) + val;
+                        const float g = a.norm_gain_dtype == ZLM_F32
+                                            ? reinterpret_cast<const float*>(a.norm_gain)[out_f]
+                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.norm_gain)[out_f]);
+                        a.norm_hb[(long)tok * a.ld_hb + out_f] = __float2bfloat16_rn(xn * (g + a.norm_offset));
+                    }
+                    const float sq = warp_sum(xn * xn);
+                    if (lane == 0) norm_red[egroup][q] = sq;
+                    if (egroup == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+                    else asm volatile("bar.sync 4, 128;" ::: "memory");
+                    if (q == 0 && lane == 0)
+                        a.norm_ssq[(long)tok * a.norm_p + tile / tok_tiles] =
+                            ((norm_red[egroup][0] + norm_red[egroup][1]) + norm_red[egroup][2]) + norm_red[egroup][3];
+                    if (egroup == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+                    else asm volatile("bar.sync 4, 128;" ::: "memory");
                 }
             }
         } else
@@ -338,7 +389,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     if (!mine) break;
-                    float val = __uint_as_float(v[j]) + bias_v;
+                    float val = __uint_as_float(v[j]);
+                    if (a.scale_ssq != nullptr) val *= inv_s[(c * 16 + j) & 63];
+                    val += bias_v;
                     if (GLU) {
                         // even lanes hold a gate row, the next lane the matching up row
                         const float up = __shfl_down_sync(0xffffffffu, val, 1);
@@ -536,10 +589,24 @@ using namespace zlm;
 //      silu(gate) * up (1) or tanh-gelu(gate) * up (2).
 // splits: 0 = choose, else the number of CTAs a tile's K range is split over (1..8).
 // Refuses (ZLM_ERR_UNSUPPORTED) strides or addresses TMA cannot read; the caller falls back.
-ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
-                           int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
-                           cudaStream_t stream) {
+//
+// An RMSNorm between two products of a step of at most 64 tokens can ride on them instead of being a kernel of
+// its own.  The product before it (accumulate into the float32 residual, K split over a cluster so that one
+// thread finishes each element) is given norm_gain / norm_hb / norm_ssq: it also writes bf16(x * gain) to
+// norm_hb [T, ld_hb] and, per token and tile row of 128 features, the sum of x^2 to norm_ssq [T, ceil(N/128)].
+// *norm_fused says whether it did (it does not when the launch it chooses has no cluster; nothing is written
+// then and the caller runs the norm kernel).  The product after it takes X = norm_hb and scale_ssq / scale_p /
+// scale_eps: every output row t is multiplied by 1 / sqrt(sum_p scale_ssq[t, p] / K + eps) before the bias.
+ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
+                                int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
+                                const void* norm_gain, int norm_gain_dtype, float norm_offset, void* norm_hb,
+                                long ld_hb, float* norm_ssq, int* norm_fused, const float* scale_ssq, int scale_p,
+                                float scale_eps, cudaStream_t stream) {
+    if (norm_fused) *norm_fused = 0;
     if (T <= 0 || N <= 0) return 0;
+    if (scale_ssq != nullptr && (T > 64 || scale_p <= 0)) return ZLM_ERR_BAD_ARG;
+    if (norm_gain != nullptr && (!accumulate || glu || !norm_hb || !norm_ssq || !norm_fused || ld_hb < N))
+        return ZLM_ERR_BAD_ARG;
     const int n_out = glu ? N / 2 : N;
     if (K <= 0 || ldx < K || ldw < K || ldy < n_out || splits < 0 || splits > 8 || glu < 0 || glu > 2)
         return ZLM_ERR_BAD_ARG;
@@ -552,6 +619,9 @@ ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int b
     a.kb_total = (K + TC_BK - 1) / TC_BK;
     a.glu_kind = glu == 2 ? 1 : 0;
     a.err = error_word();
+    a.norm_gain = nullptr; a.norm_gain_dtype = norm_gain_dtype; a.norm_offset = norm_offset;
+    a.norm_hb = (__nv_bfloat16*)norm_hb; a.ld_hb = ld_hb; a.norm_ssq = norm_ssq; a.norm_p = (N + TC_BM - 1) / TC_BM;
+    a.scale_ssq = scale_ssq; a.scale_p = scale_p; a.scale_eps = scale_eps;
     const int tiles = ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
     int s = splits;
     if (s == 0) {
@@ -568,6 +638,10 @@ ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int b
     a.kb_per_split = (a.kb_total + s - 1) / s;
     s = (a.kb_total + a.kb_per_split - 1) / a.kb_per_split;   // every rank gets at least one block
     a.splits = s;
+    if (norm_gain != nullptr && s > 1 && T <= bn) {           // a cluster and one token tile: the norm rides along
+        a.norm_gain = norm_gain;
+        *norm_fused = 1;
+    }
     // one tile per block when K is split; otherwise as many blocks as fit the GPU share the tiles
     static int sm_count = 0;
     if (sm_count == 0) {
@@ -602,6 +676,13 @@ ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int b
         case 128: return pick_mode<128>(mode, mw, mx, my, a, stream);
         default: return pick_mode<256>(mode, mw, mx, my, a, stream);
     }
+}
+
+ZLM_EXPORT int zlm_gemm_tc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
+                           int accumulate, int glu, int T, int N, int K, long ldx, long ldw, long ldy, int splits,
+                           cudaStream_t stream) {
+    return zlm_gemm_tc_norm(X, W, bias, bias_dtype, Y, y_dtype, accumulate, glu, T, N, K, ldx, ldw, ldy, splits, nullptr,
+                            ZLM_F32, 0.f, nullptr, 0, nullptr, nullptr, nullptr, 0, 0.f, stream);
 }
 
 // Reads and clears the error word the kernels report bounded-wait failures through (synchronises the device).

@@ -101,8 +101,16 @@ class Model:
         spec = self.spec
         x = step.ws.buf("residual", (step.n_tokens, spec.width), torch.float32)
         kernels.embed(self.embedding, step.tokens, x, spec.embedding_scale)
+        carried = None           # the next block's first norm, half done by the block before (steps of few tokens)
         for place, li in enumerate(spec.schedule):
-            self.blocks[li].forward(step, step.io[place], x)
+            block = self.blocks[li]
+            nxt = self.blocks[spec.schedule[place + 1]] if place + 1 < len(spec.schedule) else None
+            takes = getattr(nxt, "accepts_normed_input", None)
+            next_norm = nxt.mixer_norm if takes is not None and takes() else None
+            if carried is not None or next_norm is not None:
+                carried = block.forward(step, step.io[place], x, h_in=carried, next_norm=next_norm)
+            else:
+                block.forward(step, step.io[place], x)
         if step.n_want == 0:
             return None
         h = self.final_norm.forward(step, x, rows=step.want_rows, n_rows=step.n_want, name="final_norm_out")

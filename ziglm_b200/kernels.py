@@ -88,6 +88,9 @@ _PROTOTYPES = {
     "gemm_tc": {
         "zlm_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_long, c_long, c_long, c_int, c_void_p],
+        "zlm_gemm_tc_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_long, c_long, c_long, c_int, c_void_p, c_int, c_float, c_void_p, c_long, c_void_p,
+                             c_void_p, c_void_p, c_int, c_float, c_void_p],
         "zlm_gemm_tc_status": [c_void_p],
     },
     "sampling": {
@@ -545,14 +548,21 @@ GLU_KINDS = {"silu": 1, "gelu_tanh": 2}
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            accumulate: bool = False, splits: int = 0, glu: Optional[str] = None) -> bool:
+            accumulate: bool = False, splits: int = 0, glu: Optional[str] = None, norm_out=None, row_scale=None):
     """out[T,N] (+)= x[T,K] @ w[N,K]^T (+ bias) on the tcgen05 tensor cores, bf16 operands.
 
     With ``glu`` ("silu" or "gelu_tanh") the rows of w alternate gate and up rows and out is bf16 [T, N/2]
     holding act(gate) * up.
 
+    An RMSNorm between two products of a step of few tokens can ride on them.  ``norm_out`` = (gain, offset, hb,
+    ssq) on the product before it (``accumulate`` into the float32 residual): it also leaves bf16(x * (gain +
+    offset)) in ``hb`` [T, N] and sums of x^2 per tile row of 128 features in ``ssq`` [T, ceil(N/128)] (float32);
+    the result is then 2 if it did and 1 if the launch it chose cannot (nothing is written to hb and ssq).
+    ``row_scale`` = (ssq, eps) on the product after it, whose x is that ``hb``: every output row t is multiplied
+    by 1 / sqrt(sum(ssq[t]) / K + eps) before the bias.
+
     Returns False, having done nothing, if the operands are not what TMA can read (a row stride that is no
-    multiple of 8 elements, a base address off a 16-byte boundary).
+    multiple of 8 elements, a base address off a 16-byte boundary); else a true value.
     """
     for t, n in ((x, "x"), (w, "w"), (out, "out")):
         if not t.is_cuda:
@@ -574,14 +584,32 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
         _cuda(bias, "bias")
         if bias.numel() != N:
             raise KernelError("gemm: bias length does not match")
-    status = _fn("gemm_tc", "zlm_gemm_tc")(
+    gain = hb = ssq_out = ssq_in = None
+    offset, eps, scale_p = 0.0, 0.0, 0
+    fused = ctypes.c_int(0)
+    if norm_out is not None:
+        gain, offset, hb, ssq_out = norm_out
+        _cuda(gain, "gain"); _cuda(hb, "hb", torch.bfloat16); _cuda(ssq_out, "ssq", torch.float32)
+        if not accumulate or glu or gain.numel() != N or hb.shape != (T, N) or hb.stride(1) != 1 \
+                or ssq_out.numel() < T * (-(-N // 128)) or gain.dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError("gemm_tc: norm_out needs accumulate, a gain of N elements, hb [T, N] and ssq [T, ceil(N/128)]")
+    if row_scale is not None:
+        ssq_in, eps = row_scale
+        _cuda(ssq_in, "ssq", torch.float32)
+        if T > 64 or ssq_in.dim() != 2 or ssq_in.shape[0] < T or not ssq_in.is_contiguous():
+            raise KernelError("gemm_tc: row_scale needs at most 64 rows and ssq [T, P] contiguous")
+        scale_p = ssq_in.shape[1]
+    status = _fn("gemm_tc", "zlm_gemm_tc_norm")(
         x.data_ptr(), w.data_ptr(), _ptr(bias), code(bias.dtype) if bias is not None else F32, out.data_ptr(),
         code(out.dtype), int(accumulate), GLU_KINDS[glu] if glu else 0, T, N, K, x.stride(0) if T > 1 else K,
-        w.stride(0) if N > 1 else K, out.stride(0) if T > 1 else n_out, int(splits), _stream())
+        w.stride(0) if N > 1 else K, out.stride(0) if T > 1 else n_out, int(splits),
+        _ptr(gain), code(gain.dtype) if gain is not None else F32, float(offset), _ptr(hb),
+        hb.stride(0) if hb is not None and T > 1 else N, _ptr(ssq_out), ctypes.byref(fused), _ptr(ssq_in), scale_p,
+        float(eps), _stream())
     if status == -2:
         return False
     _check(status, "gemm_tc")
-    return True
+    return 2 if fused.value else 1
 
 
 def gemm_tc_status() -> int:
@@ -595,13 +623,15 @@ def gemm_tc_status() -> int:
     return out.value
 
 
-def fast_gemm(linear, x: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
-    """Run the product on the tensor-core kernels if they take it; False if they do not."""
+def fast_gemm(linear, x: torch.Tensor, out: torch.Tensor, accumulate: bool, norm_out=None, row_scale=None):
+    """Run the product on the tensor-core kernels if they take it (see ``gemm_tc`` for the result); False if
+    they do not."""
     if x.dtype != torch.bfloat16 or linear.weight.dtype != torch.bfloat16:
         return False
     if out.dtype not in (torch.float32, torch.bfloat16):
         return False
-    return gemm_tc(x, linear.weight, out, bias=linear.bias, accumulate=accumulate)
+    return gemm_tc(x, linear.weight, out, bias=linear.bias, accumulate=accumulate, norm_out=norm_out,
+                   row_scale=row_scale)
 
 
 # -------------------------------------------------------------------- sampling

@@ -1,4 +1,4 @@
-from .base import (KVNeed, LayerIO, ParamDecl, Part, StateNeed, block_class, feed_forward_class, mixer_class,
+from .base import (KVNeed, LayerIO, NormedInput, ParamDecl, Part, StateNeed, block_class, feed_forward_class, mixer_class,
                    norm_class, position_class, register_block, register_feed_forward, register_mixer,
                    register_norm, register_position, unregister)
 from .linear import Linear

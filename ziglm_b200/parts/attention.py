@@ -87,8 +87,13 @@ class Attention(Part):
     def state_needs(self) -> Optional[StateNeed]:
         return None
 
-    def forward(self, step, io: LayerIO, h: torch.Tensor, residual: torch.Tensor) -> None:
-        T = h.shape[0]
+    fuses_next_norm = True
+    takes_normed_input = True
+
+    def forward(self, step, io: LayerIO, h, residual: torch.Tensor, next_norm=None):
+        """``h``: the normalised rows or a half-done norm (:class:`NormedInput`).  With ``next_norm`` the output
+        projection may do the first half of that norm; the result is then its :class:`NormedInput`."""
+        T = residual.shape[0]
         n_kv_here = 0 if self.shares_cache else self.n_kv
         qkv = step.ws.buf("qkv", (T, (self.n_heads + 2 * n_kv_here) * self.head_dim), self.dtype)
         self.qkv(h, qkv)
@@ -102,13 +107,12 @@ class Attention(Part):
         out = step.ws.buf("attn_out", (T, self.n_heads * self.head_dim), self.dtype)
         if kernels.attention_with_rope(step, qkv, out, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window,
                                        io, inv_freq, rot, store):
-            self.o(out, residual, accumulate=True)
-            return
+            return self.o.accumulate_with_norm(step, out, residual, next_norm, "attn_next")
         kernels.rope_store(qkv, self.n_heads, n_kv_here, self.head_dim, rot, inv_freq, step.positions,
                            step.seq_of_token, io.block_table, io.k_pages if store else None,
                            io.v_pages if store else None, io.page_size)
         kernels.attention(step, qkv, out, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window, io)
-        self.o(out, residual, accumulate=True)
+        return self.o.accumulate_with_norm(step, out, residual, next_norm, "attn_next")
 
 
 register_mixer("attention", Attention)

@@ -17,6 +17,19 @@ Mixer           ``cache_needs() -> KVNeed | None``, ``state_needs() -> StateNeed
                 in the schedule that is running (:class:`LayerIO`).
 FeedForward     ``forward(step, h, residual)``: adds its output to ``residual``.
 Block           ``forward(step, io, x)``: runs its parts on the residual stream x.
+
+A norm that rides on its neighbours
+-----------------------------------
+In steps of a few tokens a norm kernel between two matrix products costs more in
+waiting than in work, so a part may offer to do the norm that follows it, and a
+part may accept its input normalised that way:
+``fuses_next_norm``   the part's ``forward`` takes ``next_norm=<norm part>`` and
+                      returns a :class:`NormedInput` if its last product did the
+                      norm's first half (x * gain and the sums of squares), else None;
+``takes_normed_input``the part's ``forward`` takes a :class:`NormedInput` in place
+                      of ``h`` and completes the norm in its first product.
+``fusable``           (norms) the norm is gain * x / sqrt(mean x^2 + eps) and nothing else.
+Parts without these attributes are never asked; a block falls back to the norm kernel.
 """
 from __future__ import annotations
 
@@ -60,8 +73,21 @@ class LayerIO:
     state: Optional[torch.Tensor] = None        # [n_slots, *shape]; index with step.slots
 
 
+@dataclass
+class NormedInput:
+    """A norm's input half done: ``hb`` [T, d] holds bf16(x * gain), ``ssq`` [T, P] float32 partial sums of
+    x^2 (summed over P they give the row's sum of squares).  The product that reads ``hb`` multiplies its
+    output rows by 1 / sqrt(sum(ssq[t]) / d + eps)."""
+    hb: torch.Tensor
+    ssq: torch.Tensor
+    eps: float
+
+
 class Part:
     """Base of all parts."""
+    fuses_next_norm = False
+    takes_normed_input = False
+    fusable = False
 
     def __init__(self, spec: Any, dtype: torch.dtype, device: torch.device):
         self.spec = spec

@@ -55,11 +55,26 @@ class PreNormBlock(Part):
     def state_needs(self) -> Optional[StateNeed]:
         return self.mixer.state_needs()
 
-    def forward(self, step, io: LayerIO, x: torch.Tensor) -> None:
-        h = self.mixer_norm.forward(step, x)
-        self.mixer.forward(step, io, h, x)
-        h = self.ffn_norm.forward(step, x)
+    def accepts_normed_input(self) -> bool:
+        """Whether ``forward`` may be handed this block's first norm half done (``h_in``)."""
+        return bool(self.mixer_norm.fusable and self.mixer.takes_normed_input)
+
+    def forward(self, step, io: LayerIO, x: torch.Tensor, h_in=None, next_norm=None):
+        """``h_in``: this block's first norm, half done by the block before (else the norm kernel runs).
+        ``next_norm``: the first norm of the block after; the result is its half-done form if the feed-forward's
+        last product did it, else None."""
+        h = h_in if h_in is not None else self.mixer_norm.forward(step, x)
+        if self.mixer.fuses_next_norm and self.ffn.takes_normed_input and self.ffn_norm.fusable:
+            h = self.mixer.forward(step, io, h, x, next_norm=self.ffn_norm)
+        else:
+            self.mixer.forward(step, io, h, x)
+            h = None
+        if h is None:
+            h = self.ffn_norm.forward(step, x)
+        if self.ffn.fuses_next_norm and next_norm is not None:
+            return self.ffn.forward(step, h, x, next_norm=next_norm)
         self.ffn.forward(step, h, x)
+        return None
 
 
 register_block("prenorm", PreNormBlock)

@@ -17,7 +17,7 @@ import torch
 
 from .. import kernels
 from ..config.spec import FeedForwardSpec
-from .base import ParamDecl, Part, register_feed_forward
+from .base import NormedInput, ParamDecl, Part, register_feed_forward
 from .linear import Linear
 
 
@@ -56,15 +56,23 @@ class GatedMLP(Part):
                 libs += lin.libraries(self.dtype)
         return libs
 
-    def forward(self, step, h: torch.Tensor, residual: torch.Tensor) -> None:
-        T = h.shape[0]
+    fuses_next_norm = True
+    takes_normed_input = True
+
+    def forward(self, step, h, residual: torch.Tensor, next_norm=None):
+        """``h``: the normalised rows or a half-done norm (:class:`NormedInput`).  With ``next_norm`` the down
+        projection may do the first half of that norm; the result is then its :class:`NormedInput`."""
+        T = residual.shape[0]
         act = step.ws.buf("ffn_act", (T, self.intermediate), self.dtype)
-        fused = self.interleaved and kernels.gemm_tc(h, self.gate_up.weight, act, glu=self.spec.activation)
+        normed = isinstance(h, NormedInput)
+        rows = h.hb if normed else h
+        fused = self.interleaved and kernels.gemm_tc(rows, self.gate_up.weight, act, glu=self.spec.activation,
+                                                     row_scale=(h.ssq, h.eps) if normed else None)
         if not fused:
             gu = step.ws.buf("gate_up", (T, 2 * self.intermediate), self.dtype)
             self.gate_up(h, gu)
             kernels.gated_act(gu, act, self.spec.activation, interleaved=self.interleaved)
-        self.down(act, residual, accumulate=True)
+        return self.down.accumulate_with_norm(step, act, residual, next_norm, "ffn_next")
 
 
 register_feed_forward("gated_mlp", GatedMLP)

@@ -17,6 +17,8 @@ from .base import ParamDecl, Part, register_norm
 
 
 class RMSNorm(Part):
+    fusable = True
+
     def __init__(self, spec: NormSpec, dtype: torch.dtype, device: torch.device):
         super().__init__(spec, dtype, device)
         self.width = spec.width
