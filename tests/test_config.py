@@ -126,3 +126,16 @@ def test_llama_8b_shape_counts():
                           "num_hidden_layers": 32, "num_attention_heads": 32, "num_key_value_heads": 8,
                           "vocab_size": 128256})
     assert c.parameter_count() == 8030261248
+
+
+def test_generation_config_supplies_the_stop_tokens_config_json_lacks(tmp_path):
+    import json
+    from ziglm_b200.config import config_from_folder
+    cfg = dict(helpers.TINY_A)
+    json.dump(cfg, open(tmp_path / "config.json", "w"))
+    assert config_from_folder(str(tmp_path)).model_spec().stop_token_ids == ()
+    json.dump({"eos_token_id": [5, 9], "bos_token_id": 1, "temperature": 0.6}, open(tmp_path / "generation_config.json", "w"))
+    assert tuple(config_from_folder(str(tmp_path)).model_spec().stop_token_ids) == (5, 9)
+    cfg["eos_token_id"] = 3                                  # config.json wins where it speaks
+    json.dump(cfg, open(tmp_path / "config.json", "w"))
+    assert tuple(config_from_folder(str(tmp_path)).model_spec().stop_token_ids) == (3,)

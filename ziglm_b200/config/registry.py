@@ -8,6 +8,8 @@ the class turns config.json into a typed configuration and that into a
 """
 from __future__ import annotations
 
+import json
+import os
 from typing import Any, Callable, Dict, Mapping
 
 from .llama import ConfigError, LlamaConfig, read_config_json
@@ -43,7 +45,21 @@ def config_from_dict(d: Mapping[str, Any]):
 
 
 def config_from_folder(folder: str):
-    return config_from_dict(read_config_json(folder))
+    """config.json of a model folder.  A generation_config.json beside it supplies ``eos_token_id`` and
+    ``bos_token_id`` when config.json has none (checkpoints keep the full stop set there)."""
+    d = dict(read_config_json(folder))
+    extra = os.path.join(folder, "generation_config.json")
+    if os.path.isfile(extra):
+        try:
+            with open(extra) as f:
+                gen = json.load(f)
+        except (OSError, ValueError) as e:
+            raise ConfigError(f"{extra}: cannot be read as JSON ({e})") from None
+        if isinstance(gen, dict):
+            for key in ("eos_token_id", "bos_token_id"):
+                if d.get(key) is None and gen.get(key) is not None:
+                    d[key] = gen[key]
+    return config_from_dict(d)
 
 
 register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)
