@@ -72,10 +72,13 @@ struct TcArgs {
 // Tokens staged per TMA store: the box height of the output's tensor map.
 __host__ __device__ constexpr int sub_rows(int bn) { return (bn == 16 || bn == 64) ? 16 : 32; }
 
-template <int BN> struct TcCfg {
+template <int BN, int DEEP = 0> struct TcCfg {
     // Narrow tiles (decode steps) keep few stages, so that three or four blocks fit an SM: the blocks of
     // the next product become resident while this one drains and request their weight tiles early.
-    static constexpr int STAGES = BN <= 32 ? 3 : (BN == 128 ? 5 : 4);
+    // DEEP: the gated product of a decode step runs as one tile of a megabyte of weights per block, at
+    // most two blocks per SM; what bounds it is the bytes each block has in flight, so it takes a fourth
+    // stage (measured: five and more cost the next product its early residence).
+    static constexpr int STAGES = BN <= 32 ? (DEEP ? DEEP : 3) : (BN == 128 ? 5 : 4);
     static constexpr int B_BYTES = BN * TC_BK * 2;
     static constexpr int ACC_COLS = BN;                            // columns of one accumulator
     static constexpr int COLS = 2 * BN < 32 ? 32 : 2 * BN;         // two accumulators: a power of two >= 32
@@ -107,11 +110,11 @@ __device__ __forceinline__ void grid_dependency_wait() {
 
 // Persistent: block b works on tiles b, b + gridDim.x, ...  The accumulator in tensor memory is
 // double-buffered, so the epilogue of one tile runs while the next tile's products are issued.
-template <int BN, int MODE>
+template <int BN, int MODE, int DEEP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                const __grid_constant__ CUtensorMap tmap_y, TcArgs a) {
-    using C = TcCfg<BN>;
+    using C = TcCfg<BN, DEEP>;
     constexpr int STAGES = C::STAGES;
     constexpr bool GLU = MODE == OUT_BF16_GLU || MODE == OUT_BF16_GEGLU;
     constexpr int OUT_COLS = GLU ? TC_BM / 2 : TC_BM;              // output features of a tile
@@ -535,17 +538,17 @@ static int* error_word() {
     return word;
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, int DEEP = 0>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, const TcArgs& a,
                      cudaStream_t stream) {
-    using C = TcCfg<BN>;
+    using C = TcCfg<BN, DEEP>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              C::SMEM);
         if (e != cudaSuccess) return (int)e;
         // ask for the largest shared-memory carve-out, so that two blocks of the narrow tiles fit an SM
-        e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, DEEP>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -564,7 +567,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const CUtenso
     attr[1].val.clusterDim.z = a.splits;
     cfg.attrs = attr;
     cfg.numAttrs = a.splits > 1 ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, MODE>, mw, mx, my, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, MODE, DEEP>, mw, mx, my, a);
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
@@ -574,8 +577,12 @@ static int pick_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, con
     switch (mode) {
         case OUT_F32: return launch_tc<BN, OUT_F32>(mw, mx, my, a, s);
         case OUT_F32_ACC: return launch_tc<BN, OUT_F32_ACC>(mw, mx, my, a, s);
-        case OUT_BF16_GLU: return launch_tc<BN, OUT_BF16_GLU>(mw, mx, my, a, s);
-        case OUT_BF16_GEGLU: return launch_tc<BN, OUT_BF16_GEGLU>(mw, mx, my, a, s);
+        case OUT_BF16_GLU:
+            if (BN <= 32 && a.splits == 1 && a.grid_x <= 2 * 148) return launch_tc<BN, OUT_BF16_GLU, 4>(mw, mx, my, a, s);
+            return launch_tc<BN, OUT_BF16_GLU>(mw, mx, my, a, s);
+        case OUT_BF16_GEGLU:
+            if (BN <= 32 && a.splits == 1 && a.grid_x <= 2 * 148) return launch_tc<BN, OUT_BF16_GEGLU, 4>(mw, mx, my, a, s);
+            return launch_tc<BN, OUT_BF16_GEGLU>(mw, mx, my, a, s);
         default: return launch_tc<BN, OUT_BF16>(mw, mx, my, a, s);
     }
 }
