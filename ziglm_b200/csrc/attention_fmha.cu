@@ -12,9 +12,9 @@
 // the cache stores them) in the order  P_0 V, S_0 of the next step, P_1 V, S_1 of the next step, so
 // that the tensor core works for one tile while the softmax of the other runs; warps 2-5 are the
 // softmax of tile 0 and warps 6-9 of tile 1: thread r owns query row r, reads its row of S with
-// tcgen05.ld (twice: for the maximum, then for the exponentials, 32 columns at a time, which keeps
-// registers free), keeps the running maximum and sum in float (base 2, scale folded in), writes the
-// probabilities with tcgen05.st, and rescales O in tensor memory when its maximum has moved by more
+// tcgen05.ld (all 128 scores issued together and waited for once; the row stays in registers between
+// the maximum and the exponentials), keeps the running maximum and sum in float (base 2, scale folded
+// in), writes the probabilities with tcgen05.st, and rescales O in tensor memory when its maximum has moved by more
 // than 2^8 (a rescale that is skipped leaves probabilities up to 256, well inside bf16 and float
 // range, and cancels in O / l).  The tensor core runs its instructions in the order of issue, so when
 // S_t of a step is there, P_t V of the step before is complete: the softmax may touch O_t and
@@ -72,6 +72,76 @@ struct FmArgs {
     const int* past_lens;
     int* err;
 };
+
+// The softmax of one query row over a step of NP pages: S from tensor memory, P (bf16) back over its first
+// half.  Returns the factor by which the running sum was rescaled; updates m (reference maximum, base 2) and l.
+template <int HD, int NP>
+__device__ __forceinline__ float softmax_row(uint32_t t_s, uint32_t t_o, bool full, int lo_vis, int hi_vis, float scale,
+                                             float neg_big, int lt, float& m, float& l) {
+    constexpr int N = NP * FM_PAGE;
+    uint32_t v[N];
+#pragma unroll
+    for (int c = 0; c < N / 32; ++c) tmem_ld32(t_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+    tmem_ld_wait();
+    float mx8[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx8[i] = neg_big;
+    if (full) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(v[i]));
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            if (i < lo_vis || i > hi_vis) v[i] = __float_as_uint(neg_big);      // stays masked below
+            mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(v[i]));
+        }
+    }
+    const float mx_raw = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                               fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+    const float mx = mx_raw == neg_big ? -INFINITY : mx_raw * scale;       // the scale is positive
+    // the reference maximum moves only when the true one has grown by more than 8 (in base 2)
+    float corr = 1.0f;
+    if (mx > m + 8.0f) {
+        corr = exp2f(m - mx);                                   // 0 the first time (m = -inf)
+        m = mx;
+    }
+    const float use = m == -INFINITY ? 0.f : m;
+    // rescale O when some row of the warp moved its reference (never in the first step: O is empty)
+    if (lt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_o + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st32(t_o + c * 32, o);
+        }
+    }
+    // stage by stage over the row: neighbouring instructions never depend on one another
+    float sum8[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum8[i] = 0.f;
+#pragma unroll
+    for (int c = 0; c < N / 32; ++c) {
+        float x[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = fmaf(__uint_as_float(v[c * 32 + i]), scale, -use);   // masked: about -3e38
+#pragma unroll
+        for (int i = 0; i < 32; ++i) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(x[i]) : "f"(x[i]));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sum8[i & 7] += x[i];
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 pp = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            pk[i] = *reinterpret_cast<uint32_t*>(&pp);
+        }
+        tmem_st16(t_s + c * 16, pk);
+    }
+    l = l * corr + (((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7])));
+    return corr;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(FM_THREADS, 1)
@@ -298,84 +368,15 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             const int key_end = key0 + np * FM_PAGE - 1;               // last key this step really holds
             const bool full = key0 >= start && key_end <= pos;
             const int lo_vis = max(start, key0) - key0, hi_vis = min(pos, key_end) - key0;   // visible keys [lo, hi]
-            // first reading: the row's maximum (eight independent chains, so that one warp alone keeps its
-            // pipe busy)
-            float mx8[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) mx8[i] = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < np * (FM_PAGE / 32); ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_s + c * 32, v);
-                tmem_ld_wait();
-                if (full) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(v[i]));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int k = c * 32 + i;
-                        const float x = (k >= lo_vis && k <= hi_vis) ? __uint_as_float(v[i]) : neg_big;
-                        mx8[i & 7] = fmaxf(mx8[i & 7], x);
-                    }
-                }
-            }
-            float mx_raw = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                                 fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-            const float mx = mx_raw == neg_big ? -INFINITY : mx_raw * scale;       // the scale is positive
-            // the reference maximum moves only when the true one has grown by more than 8 (in base 2)
-            float corr = 1.0f;
-            if (mx > m + 8.0f) {
-                corr = exp2f(m - mx);                                   // 0 the first time (m = -inf)
-                m = mx;
-            }
-            const float use = m == -INFINITY ? 0.f : m;
-            // rescale O when some row of the warp moved its reference (never in the first step: O is empty)
-            if (lt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-#pragma unroll 1
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(t_o + c * 32, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                    tmem_st32(t_o + c * 32, v);
-                }
-            }
-            // second reading: exponentials, their sum, and P as bf16 over the first half of the S columns
-            // (chunk c of 32 scores becomes 16 columns at 16 c, always behind the scores still to be read)
-            float sum8[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sum8[i] = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < np * (FM_PAGE / 32); ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_s + c * 32, v);
-                tmem_ld_wait();
-                float x[32];
-                // stage by stage over the 32 scores: neighbouring instructions never depend on one another
-#pragma unroll
-                for (int i = 0; i < 32; ++i) x[i] = fmaf(__uint_as_float(v[i]), scale, -use);
-                if (!full) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int k = c * 32 + i;
-                        if (k < lo_vis || k > hi_vis) x[i] = -INFINITY;
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(x[i]) : "f"(x[i]));
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sum8[i & 7] += x[i];
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    __nv_bfloat162 pp = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-                    pk[i] = *reinterpret_cast<uint32_t*>(&pp);
-                }
-                tmem_st16(t_s + c * 16, pk);
-            }
-            l = l * corr + (((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7])));
+            // One reading of the row: the loads of all its scores are issued together and waited for once
+            // (a tcgen05.ld and its wait cost about as much as the arithmetic on 32 scores), the row stays in
+            // registers between the maximum and the exponentials, and the stores of P are waited for once.
+            float corr;
+            if (np == FM_NP)
+                corr = softmax_row<HD, FM_NP>(t_s, t_o, full, lo_vis, hi_vis, scale, neg_big, lt, m, l);
+            else
+                corr = softmax_row<HD, 1>(t_s, t_o, full, lo_vis, hi_vis, scale, neg_big, lt, m, l);
+            (void)corr;
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
