@@ -11,6 +11,8 @@ reference's single-sequence calls expressed through ``step``.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -301,7 +303,7 @@ class _DecodeGraph:
     """The captured launches of a decode step of one batch size, with the memory they point to."""
 
     def __init__(self, engine: Engine, batch: int):
-        self.engine = engine
+        self._engine = weakref.ref(engine)      # the engine owns this object: no cycle, both go when it is dropped
         self.batch = batch
         width = engine.cache.max_pages_per_seq
         self.layout = BatchLayout(batch, batch, batch, tuple(width for _ in engine.cache.groups))
@@ -314,6 +316,13 @@ class _DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.kernels_per_replay = 0
+
+    @property
+    def engine(self) -> Engine:
+        e = self._engine()
+        if e is None:
+            raise RuntimeError("the engine of this decode graph is gone")
+        return e
 
     def staging(self) -> torch.Tensor:
         self.flip ^= 1
@@ -342,8 +351,17 @@ class _DecodeGraph:
         self.kernels_per_replay = kernels.launches() - before
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            captured = e.model.forward(self._context(past, slots))
+        # Nothing may destroy another graph while this one is being captured: an engine dropped earlier takes
+        # its graphs with it only when the collector runs, and that must not be in the middle of the capture.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                captured = e.model.forward(self._context(past, slots))
+        finally:
+            if collecting:
+                gc.enable()
         kernels.reset_launches_by(self.kernels_per_replay)
         assert captured.data_ptr() == logits.data_ptr()
         self.graph, self.logits = graph, logits
