@@ -2,6 +2,8 @@
 """Decode and prefill throughput of the Llama-3.1-8B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+    python bench.py --case prefill|decode [--layers L] [--batch B] [--context C]    one phase alone, for profilers
+    python bench.py --case reference-kernels [--context C]     the reference's CUDA kernels alone, if they were built
 
 A "step" is one decode step of a batch of 8 sequences at a context of 4096
 tokens.  ``value`` is decoded tokens a second, timed on the device with CUDA
