@@ -171,8 +171,8 @@ def test_attention_decode_flat_many_tokens(K):
 @pytest.mark.parametrize("hd,rot", [(64, 64), (128, 128), (128, 64), (64, 0)])
 @pytest.mark.parametrize("nh,nkv", [(8, 2), (6, 3)])
 @pytest.mark.parametrize("store", [True, False])
-@pytest.mark.parametrize("n_blocks", [0, 5])
-def test_attention_decode_flat_with_rotation_and_cache_write(K, hd, rot, nh, nkv, store, n_blocks):
+@pytest.mark.parametrize("n_blocks,window", [(0, None), (5, None), (5, 100)])
+def test_attention_decode_flat_with_rotation_and_cache_write(K, hd, rot, nh, nkv, store, n_blocks, window):
     """The flat kernel doing the step's rotation and cache write itself, against rope_store followed by the
     same kernel without them: the same output, the same rows in the cache, qkv left as it was.  Positions at
     the start, the end and the middle of a page; the cache row of the new token holds poison beforehand."""
@@ -205,7 +205,7 @@ def test_attention_decode_flat_with_rotation_and_cache_write(K, hd, rot, nh, nkv
         if not fused:
             K.rope_store(rows, nh, nkv if store else 0, hd, rot, inv, positions, seq, table,
                          k_pages if store else None, v_pages if store else None, 64)
-        assert K.attention_decode_flat(rows, out, nh, nkv, hd, scale, None, positions, seq, table, k_pages, v_pages,
+        assert K.attention_decode_flat(rows, out, nh, nkv, hd, scale, window, positions, seq, table, k_pages, v_pages,
                                        64, nb, counters, scratch, rope=(inv, rot, store) if fused else None)
         torch.cuda.synchronize()
         assert K.attention_tc_status() == 0 and int(counters.abs().sum()) == 0
