@@ -269,3 +269,33 @@ def test_tensor_core_head_sizes_take_the_tensor_core_attention(zoo, name, monkey
     # A norm whose neighbours carry it (a product wide enough to be split over a cluster before it) is no launch.
     assert 5 * layers + 3 <= kernels.launches() - before <= 7 * layers + 3
     assert kernels.attention_tc_status() == 0 and kernels.attention_fmha_status() == 0
+
+
+def test_a_decode_step_taken_again_is_the_same_step(zoo):
+    """When the same sequences bring one token each again, the engine reuses the packed integers of the step
+    before (only tokens and lengths change) until a sequence stands at a page boundary: the logits are those of
+    an engine that packs every step anew, over 150 steps that cross boundaries at different times."""
+    from ziglm_b200 import Engine, EngineOptions
+    folder, eng = zoo.get("D", "bfloat16")
+    plain = Engine.load(folder, EngineOptions(dtype="bfloat16", max_tokens=1024, max_batch=8, use_graphs=False))
+    V = helpers.CONFIGS["D"]["vocab_size"]
+    prompts = [helpers.random_tokens(n, V, 70 + n) for n in (3, 60, 41)]
+    a = [eng.alloc_slot() for _ in prompts]
+    b = [plain.alloc_slot() for _ in prompts]
+    eng.step(list(zip(a, prompts)))
+    plain.step(list(zip(b, prompts)))
+    taken_again = 0
+    for k in range(150):
+        toks = helpers.random_tokens(3, V, 1000 + k)
+        if eng._repeat is not None and eng._repeat.left > 0:
+            taken_again += 1
+        got = eng.step([(s, [t]) for s, t in zip(a, toks)]).clone()
+        want = plain.step([(s, [t]) for s, t in zip(b, toks)]).clone()
+        assert torch.equal(got, want), f"step {k}"
+        assert [eng.length(s) for s in a] == [plain.length(s) for s in b]
+    assert 100 < taken_again < 150                   # most steps, but not those at a page boundary
+    for s in a:
+        eng.free_slot(s)
+    for s in b:
+        plain.free_slot(s)
+    eng.cache.slots.check()

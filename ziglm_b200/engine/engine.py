@@ -94,6 +94,7 @@ class Engine:
         self._dev: Optional[torch.Tensor] = None
         self._flip = 0
         self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._repeat: Optional["_RepeatedDecode"] = None      # the last decode step, ready to be taken once more
         self._graph_kernels = 0
         self.last_step_h2d_bytes = 0
         self._default_slot: Optional[int] = None
@@ -138,9 +139,11 @@ class Engine:
 
     # ------------------------------------------------------------------- slots
     def alloc_slot(self) -> int:
+        self._repeat = None
         return self.cache.alloc_slot()
 
     def free_slot(self, slot: int) -> None:
+        self._repeat = None
         self.cache.free_slot(slot)
 
     def length(self, slot: int) -> int:
@@ -164,6 +167,11 @@ class Engine:
         """
         if not entries:
             raise StepError("a step needs at least one sequence")
+        if want is None and self._repeat is not None:
+            logits = self._repeat_decode(entries)
+            if logits is not None:
+                return logits
+        self._repeat = None
         slots = [int(s) for s, _ in entries]
         new_tokens = [list(t) for _, t in entries]
         if len(set(slots)) != len(slots):
@@ -199,6 +207,7 @@ class Engine:
         if single and want_rows == list(range(B)) and self.options.use_graphs:
             logits = self._graph_step(slots, past, new_tokens, want_rows)
             self.cache.slots.advance(growth)
+            self._arm_repeat(slots, want is None or all(list(w) == [0] for w in want))
             return logits
         width = -(-max_total // self.cache.page_size)
         widths = tuple(width for _ in self.cache.groups)
@@ -250,6 +259,52 @@ class Engine:
         self.last_step_h2d_bytes = g.layout.total * 4
         return g.run(past, slots)
 
+    # ---------------------------------------------- the same decode step once more
+    def _arm_repeat(self, slots: List[int], plain_want: bool) -> None:
+        """After a decode step of a batch: if the same sequences bring one token each again, nothing of the
+        step's integers changes but the tokens and the lengths, as long as no sequence needs a new page, no
+        group lets pages go behind a window and no sequence reaches its limit."""
+        self._repeat = None
+        if not plain_want or any(g.pages.window is not None for g in self.cache.groups):
+            return
+        page = self.cache.page_size
+        lengths = [self.cache.slots.length_of(s) for s in slots]
+        # steps that can be taken before some sequence stands at a page boundary or at the length limit
+        left = min(min((page - L % page) % page for L in lengths), self.max_seq_len - max(lengths))
+        if left <= 0:
+            return
+        g = self._graphs[len(slots)]
+        self._repeat = _RepeatedDecode(list(slots), g, g.host[g.flip].numpy().copy(), left)
+
+    def _repeat_decode(self, entries) -> Optional[torch.Tensor]:
+        r = self._repeat
+        if len(entries) != len(r.slots) or r.left <= 0:
+            return None
+        tokens = []
+        for (slot, toks), known in zip(entries, r.slots):
+            if slot != known or len(toks) != 1:
+                return None
+            tokens.append(toks[0])
+        if min(tokens) < 0 or max(tokens) >= self.spec.vocab_size:
+            return None                                   # the general path names the offender
+        g, o, B = r.graph, r.graph.layout.offsets, len(tokens)
+        image = r.image
+        image[o["tokens"]:o["tokens"] + B] = tokens
+        for name in ("positions", "past_lens", "total_lens"):
+            image[o[name]:o[name] + B] += 1
+        host = g.staging()
+        host.numpy()[:] = image
+        g.dev.copy_(host, non_blocking=True)
+        g.mark_copied()
+        self.last_step_h2d_bytes = g.layout.total * 4
+        g.graph.replay()
+        self._graph_kernels += g.kernels_per_replay
+        length = self.cache.slots.length
+        for slot in r.slots:
+            length[slot] += 1
+        r.left -= 1
+        return g.logits
+
     def graph_launched_kernels(self) -> int:
         """Kernels launched by graph replays since the counter was last read."""
         n, self._graph_kernels = self._graph_kernels, 0
@@ -297,6 +352,16 @@ class Engine:
     def generate(self, prompts, options=None, callback=None):
         from .generate import generate
         return generate(self, prompts, options, callback)
+
+
+@dataclass
+class _RepeatedDecode:
+    """A decode step that may be taken again as it is: its sequences, its graph, the packed integers of the
+    step that was just run (as they lie in the staging buffer) and how many more steps keep them valid."""
+    slots: List[int]
+    graph: "_DecodeGraph"
+    image: "object"
+    left: int
 
 
 class _DecodeGraph:
