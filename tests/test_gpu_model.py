@@ -273,8 +273,8 @@ def test_tensor_core_head_sizes_take_the_tensor_core_attention(zoo, name, monkey
 
 def test_a_decode_step_taken_again_is_the_same_step(zoo):
     """When the same sequences bring one token each again, the engine reuses the packed integers of the step
-    before (only tokens and lengths change) until a sequence stands at a page boundary: the logits are those of
-    an engine that packs every step anew, over 150 steps that cross boundaries at different times."""
+    before (tokens and lengths change, and one table entry when a sequence starts a page): the logits are those
+    of an engine that packs every step anew, over 150 steps that cross page boundaries at different times."""
     from ziglm_b200 import Engine, EngineOptions
     folder, eng = zoo.get("D", "bfloat16")
     plain = Engine.load(folder, EngineOptions(dtype="bfloat16", max_tokens=1024, max_batch=8, use_graphs=False))
@@ -293,7 +293,7 @@ def test_a_decode_step_taken_again_is_the_same_step(zoo):
         want = plain.step([(s, [t]) for s, t in zip(b, toks)]).clone()
         assert torch.equal(got, want), f"step {k}"
         assert [eng.length(s) for s in a] == [plain.length(s) for s in b]
-    assert 100 < taken_again < 150                   # most steps, but not those at a page boundary
+    assert taken_again >= 148                        # every step after the first decode step
     for s in a:
         eng.free_slot(s)
     for s in b:

@@ -17,6 +17,7 @@ import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -262,19 +263,18 @@ class Engine:
     # ---------------------------------------------- the same decode step once more
     def _arm_repeat(self, slots: List[int], plain_want: bool) -> None:
         """After a decode step of a batch: if the same sequences bring one token each again, nothing of the
-        step's integers changes but the tokens and the lengths, as long as no sequence needs a new page, no
-        group lets pages go behind a window and no sequence reaches its limit."""
+        step's integers changes but the tokens, the lengths and, for a sequence that stands at a page boundary,
+        one entry of its block table, as long as no group lets pages go behind a window and no sequence
+        reaches its limit."""
         self._repeat = None
         if not plain_want or any(g.pages.window is not None for g in self.cache.groups):
             return
-        page = self.cache.page_size
-        lengths = [self.cache.slots.length_of(s) for s in slots]
-        # steps that can be taken before some sequence stands at a page boundary or at the length limit
-        left = min(min((page - L % page) % page for L in lengths), self.max_seq_len - max(lengths))
+        lengths = np.array([self.cache.slots.length_of(s) for s in slots], dtype=np.int64)
+        left = self.max_seq_len - int(lengths.max())
         if left <= 0:
             return
         g = self._graphs[len(slots)]
-        self._repeat = _RepeatedDecode(list(slots), g, g.host[g.flip].numpy().copy(), left)
+        self._repeat = _RepeatedDecode(list(slots), g, g.host[g.flip].numpy().copy(), left, lengths)
 
     def _repeat_decode(self, entries) -> Optional[torch.Tensor]:
         r = self._repeat
@@ -288,7 +288,16 @@ class Engine:
         if min(tokens) < 0 or max(tokens) >= self.spec.vocab_size:
             return None                                   # the general path names the offender
         g, o, B = r.graph, r.graph.layout.offsets, len(tokens)
-        image = r.image
+        image, page = r.image, self.cache.page_size
+        at_boundary = np.nonzero(r.lengths % page == 0)[0]
+        if at_boundary.size:
+            # these sequences start a page with this token: take the pages (all or none) and enter them
+            self.cache.slots.reserve({r.slots[b]: 1 for b in at_boundary})
+            for gi, grp in enumerate(self.cache.groups):
+                width = g.layout.table_widths[gi]
+                for b in at_boundary:
+                    idx = int(r.lengths[b]) // page
+                    image[o[f"table{gi}"] + int(b) * width + idx] = grp.pages.pages_of[r.slots[b]][idx]
         image[o["tokens"]:o["tokens"] + B] = tokens
         for name in ("positions", "past_lens", "total_lens"):
             image[o[name]:o[name] + B] += 1
@@ -302,6 +311,7 @@ class Engine:
         length = self.cache.slots.length
         for slot in r.slots:
             length[slot] += 1
+        r.lengths += 1
         r.left -= 1
         return g.logits
 
@@ -362,6 +372,7 @@ class _RepeatedDecode:
     graph: "_DecodeGraph"
     image: "object"
     left: int
+    lengths: "object"        # int64 array: the sequences' lengths
 
 
 class _DecodeGraph:
