@@ -97,36 +97,67 @@ __device__ __forceinline__ float block_exclusive_scan_f(float v, float* warp_tot
 }
 
 // ------------------------------------------------------------------- argmax
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+// A row of a large vocabulary is half a megabyte: one block walking it alone is bound by its own load
+// latency.  ARGMAX_PARTS blocks take a slice each and leave their best (value, id) in a device array of the
+// library; the block that arrives last at the row's counter picks among them and sets the counter back to zero
+// (no block waits for another; nothing is allocated).  The lowest id wins ties, also across slices.
+constexpr int ARGMAX_PARTS = 32;
+constexpr int ARGMAX_THREADS = 256;
+constexpr int ARGMAX_MAX_ROWS = 4096;           // rows per launch; the host loops over more
+static __device__ float g_argmax_val[ARGMAX_MAX_ROWS * ARGMAX_PARTS];
+static __device__ int g_argmax_idx[ARGMAX_MAX_ROWS * ARGMAX_PARTS];
+static __device__ int g_argmax_count[ARGMAX_MAX_ROWS];
+
+__device__ __forceinline__ void better(float& best, int& bi, float ov, int oi) {
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+}
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
 argmax_kernel(const float* __restrict__ logits, int V, long row_stride, int* __restrict__ out) {
-    __shared__ float vals[32];
-    __shared__ int idxs[32];
-    const float* row = logits + (long)blockIdx.x * row_stride;
+    __shared__ float vals[ARGMAX_THREADS / 32];
+    __shared__ int idxs[ARGMAX_THREADS / 32];
+    __shared__ int last_s;
+    const int r = blockIdx.y, part = blockIdx.x;
+    const float* row = logits + (long)r * row_stride;
+    const int per = (V + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+    const int lo = min(V, part * per), hi = min(V, lo + per);
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += ARGMAX_THREADS) {
         const float v = row[i];
-        if (v > best || bi == 0x7fffffff) { best = v; bi = i; }
+        if (v > best || bi == 0x7fffffff) { best = v; bi = i; }       // ids rise within a thread: ties keep the lower
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1)
+        better(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
     if (lane == 0) { vals[warp] = best; idxs[warp] = bi; }
     __syncthreads();
     if (warp == 0) {
-        best = lane < (blockDim.x >> 5) ? vals[lane] : -INFINITY;
-        bi = lane < (blockDim.x >> 5) ? idxs[lane] : 0x7fffffff;
+        best = lane < ARGMAX_THREADS / 32 ? vals[lane] : -INFINITY;
+        bi = lane < ARGMAX_THREADS / 32 ? idxs[lane] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) { best = ov; bi = oi; }
+        for (int o = 16; o > 0; o >>= 1)
+            better(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (lane == 0) {
+            g_argmax_val[r * ARGMAX_PARTS + part] = best;
+            g_argmax_idx[r * ARGMAX_PARTS + part] = bi;
+            __threadfence();
+            last_s = atomicAdd(&g_argmax_count[r], 1) == ARGMAX_PARTS - 1;
         }
-        if (lane == 0) out[blockIdx.x] = bi;
+        __syncwarp();
+        if (last_s) {                       // read by the warp that wrote it
+            __threadfence();
+            best = __ldcg(&g_argmax_val[r * ARGMAX_PARTS + lane]);
+            bi = __ldcg(&g_argmax_idx[r * ARGMAX_PARTS + lane]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                better(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+            if (lane == 0) {
+                out[r] = bi;
+                g_argmax_count[r] = 0;
+            }
+        }
     }
 }
 
@@ -341,7 +372,12 @@ using namespace zlm;
 ZLM_EXPORT int zlm_argmax(const float* logits, int rows, int V, long row_stride, int* out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (V <= 0 || row_stride < V) return ZLM_ERR_BAD_ARG;
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, V, row_stride, out);
+    static_assert(ARGMAX_PARTS == 32, "the last block reads one partial result per lane");
+    for (int r0 = 0; r0 < rows; r0 += ARGMAX_MAX_ROWS) {
+        const int n = rows - r0 < ARGMAX_MAX_ROWS ? rows - r0 : ARGMAX_MAX_ROWS;
+        argmax_kernel<<<dim3(ARGMAX_PARTS, n), ARGMAX_THREADS, 0, stream>>>(logits + (long)r0 * row_stride, V, row_stride,
+                                                                           out + r0);
+    }
     return launch_status();
 }
 
