@@ -328,6 +328,27 @@ def test_sample_follows_the_chain(K, temperature, top_k, top_p, min_p):
     assert solo.item() == got[7]
 
 
+def test_sample_with_changing_row_counts_and_a_wide_vocabulary(K):
+    """The sampler keeps scratch between calls: calls with 1, 40, 3 and 40 rows, one after another, must each
+    give the plain draw.  The vocabulary is wide enough that a row is cut into slices over several blocks."""
+    from ziglm_b200.sampling import uniform01
+    V, most = 12007, 40
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(most, V, generator=g) * 2.0
+    rng = torch.tensor([[77 + 5 * r, r] for r in range(most)], dtype=torch.int64)
+    hist = torch.randint(0, V, (most, 64), generator=g, dtype=torch.int32)
+    want = []
+    for r in range(most):
+        row = P.apply_penalties(logits[r], hist[r].tolist(), 1.1, 0.0, 64)
+        want.append(P.sample(row, uniform01(77 + 5 * r, r), 0.8, 40, 0.95, 0.02))
+    for rows in (1, most, 3, most):
+        d = logits[:rows].to(DEV)
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        K.sample(d, out, rng[:rows].to(DEV), 0.8, 40, 0.95, 0.02, 1.1, 0.0, hist[:rows].to(DEV))
+        got = out.tolist()
+        assert sum(a != b for a, b in zip(got, want)) <= (1 if rows > 8 else 0), (rows, got, want[:rows])
+
+
 def test_sample_distribution_and_ties(K):
     V, n = 6, 4000
     logits = torch.tensor([0.0, 1.0, 2.0, 0.5, -1.0, 2.0]).repeat(n, 1)

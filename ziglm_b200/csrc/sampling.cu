@@ -365,9 +365,253 @@ sample_kernel(float* __restrict__ logits, int V, long row_stride, SampleArgs a, 
     }
 }
 
+// ------------------------------------------------------- sample, many blocks per row
+// The chain with 1 <= top_k <= 64 on a large vocabulary.  SP_PARTS blocks take a slice of the row each: they
+// apply the penalties of the ids in their slice, keep the scaled logits of the slice in shared memory, find
+// its maximum, its sum of exponentials and its k best candidates exactly (radix select in shared memory,
+// ties to the lower id), and leave them in scratch.  The global k best are among those: the block that
+// arrives last at the row's counter sorts the SP_PARTS * k candidates by (logit descending, id ascending),
+// forms the row's maximum and denominator from the slices' and cuts and draws as sample_kernel does.
+constexpr int SP_PARTS = 32;
+constexpr int SP_THREADS = 256;
+constexpr int SP_KMAX = 64;
+constexpr int SP_SORT = SP_PARTS * SP_KMAX;          // 2048 candidates, a power of two
+
+__global__ void __launch_bounds__(SP_THREADS)
+sample_parts_kernel(float* __restrict__ logits, int V, long row_stride, SampleArgs a, const int* __restrict__ history,
+                    const long long* __restrict__ rng, int* __restrict__ out, int* __restrict__ counters,
+                    float* __restrict__ pmax, float* __restrict__ psum, float* __restrict__ cz, int* __restrict__ cid) {
+    extern __shared__ float dyn[];
+    __shared__ float fscratch[33];
+    __shared__ int iscratch[32];
+    __shared__ int itotal;
+    __shared__ int hist[256];
+    __shared__ unsigned prefix_s;
+    __shared__ int remaining_s;
+    __shared__ int n_cand;
+    __shared__ int last_s;
+    const int tid = threadIdx.x, r = blockIdx.y, part = blockIdx.x;
+    float* row = logits + (long)r * row_stride;
+    const int per = (V + SP_PARTS - 1) / SP_PARTS;
+    const int lo = min(V, part * per), hi = min(V, lo + per), n = hi - lo;
+    float* z = dyn;                                       // [per] scaled logits of the slice
+
+    // 0. penalties of the ids of this slice, once per id, occurrences in window order (as sample_kernel)
+    if (a.window > 0 && (a.repetition_penalty != 1.0f || a.presence_penalty != 0.0f)) {
+        const int* h = history + (long)r * a.window;
+        if (tid < a.window) {
+            const int tok = h[tid];
+            bool first = tok >= lo && tok < hi;
+            for (int j = 0; j < tid && first; ++j) first = h[j] != tok;
+            if (first) {
+                float l = row[tok];
+                for (int j = tid; j < a.window; ++j) {
+                    if (h[j] != tok) continue;
+                    l = l > 0.f ? l / a.repetition_penalty : l * a.repetition_penalty;
+                    l -= a.presence_penalty;
+                }
+                row[tok] = l;
+            }
+        }
+        __syncthreads();
+    }
+    // 1. the slice, its maximum and its sum of exponentials
+    float m = -INFINITY;
+    for (int i = tid; i < n; i += SP_THREADS) {
+        const float v = row[lo + i] * a.inv_temperature;
+        z[i] = v;
+        m = fmaxf(m, v);
+    }
+    m = block_max(m, fscratch);
+    float part_sum = 0.f;
+    for (int i = tid; i < n; i += SP_THREADS) part_sum += expf(z[i] - m);
+    part_sum = block_sum(part_sum, fscratch);
+    // 2. the k best of the slice, exactly
+    const int k = min(a.top_k, n);
+    if (tid == 0) { prefix_s = 0u; remaining_s = k; }
+    __syncthreads();
+    for (int pass = 0; pass < 4 && k > 0; ++pass) {
+        const int shift = 24 - 8 * pass;
+        hist[tid] = 0;
+        __syncthreads();
+        const unsigned prefix = prefix_s;
+        const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int i = tid; i < n; i += SP_THREADS) {
+            const unsigned key = orderable(z[i]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int rem = remaining_s;
+            int b = 255;
+            for (; b > 0; --b) {
+                if (hist[b] >= rem) break;
+                rem -= hist[b];
+            }
+            prefix_s = prefix | ((unsigned)b << shift);
+            remaining_s = rem;
+        }
+        __syncthreads();
+    }
+    const unsigned kth = prefix_s;
+    const int ties_needed = remaining_s;
+    float* my_cz = cz + ((long)r * SP_PARTS + part) * SP_KMAX;
+    int* my_cid = cid + ((long)r * SP_PARTS + part) * SP_KMAX;
+    if (tid == 0) n_cand = 0;
+    __syncthreads();
+    // contiguous runs per thread, so that ties are taken in id order
+    const int run = (n + SP_THREADS - 1) / SP_THREADS;
+    const int t_lo = min(n, tid * run), t_hi = min(n, t_lo + run);
+    int my_ties = 0;
+    for (int i = t_lo; i < t_hi && k > 0; ++i) {
+        const unsigned key = orderable(z[i]);
+        if (key > kth) {
+            const int slot = atomicAdd(&n_cand, 1);
+            my_cz[slot] = z[i];
+            my_cid[slot] = lo + i;
+        } else if (key == kth) {
+            ++my_ties;
+        }
+    }
+    // exclusive scan of the ties over the 256 threads (8 warps)
+    int tie_rank;
+    {
+        const int lane = tid & 31, warp = tid >> 5;
+        int inc = my_ties;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += v;
+        }
+        __syncthreads();
+        if (lane == 31) iscratch[warp] = inc;
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += iscratch[w];
+        tie_rank = before + inc - my_ties;
+    }
+    __syncthreads();
+    const int n_above = n_cand;
+    {
+        int rank = tie_rank;
+        for (int i = t_lo; i < t_hi && rank < ties_needed; ++i) {
+            if (orderable(z[i]) == kth) {
+                my_cz[n_above + rank] = z[i];
+                my_cid[n_above + rank] = lo + i;
+                ++rank;
+            }
+        }
+    }
+    for (int i = k + tid; i < SP_KMAX; i += SP_THREADS) { my_cz[i] = -INFINITY; my_cid[i] = 0x7fffffff; }
+    if (tid == 0) { pmax[r * SP_PARTS + part] = m; psum[r * SP_PARTS + part] = part_sum; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) last_s = atomicAdd(&counters[r], 1) == SP_PARTS - 1;
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+
+    // ---- the last block of the row: maximum and denominator of the row, in slice order
+    float* sz = dyn;                                       // [SP_SORT]
+    int* sid = reinterpret_cast<int*>(dyn + SP_SORT);      // [SP_SORT]
+    float row_max, denom;
+    {
+        float mp = tid < SP_PARTS ? __ldcg(&pmax[r * SP_PARTS + tid]) : -INFINITY;
+        row_max = block_max(mp, fscratch);
+        float sp = tid < SP_PARTS ? __ldcg(&psum[r * SP_PARTS + tid]) * expf(mp - row_max) : 0.f;
+        denom = block_sum(sp, fscratch);
+    }
+    for (int i = tid; i < SP_SORT; i += SP_THREADS) {
+        sz[i] = __ldcg(&cz[(long)r * SP_SORT + i]);
+        sid[i] = __ldcg(&cid[(long)r * SP_SORT + i]);
+    }
+    __syncthreads();
+    for (int size = 2; size <= SP_SORT; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = tid; i < SP_SORT; i += SP_THREADS) {
+                const int j = i ^ stride;
+                if (j > i) {
+                    const bool up = (i & size) == 0;
+                    const float zi = sz[i], zj = sz[j];
+                    const int ii = sid[i], ij = sid[j];
+                    const bool i_first = zi > zj || (zi == zj && ii < ij);
+                    if (i_first != up) { sz[i] = zj; sz[j] = zi; sid[i] = ij; sid[j] = ii; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid == 0) {
+        const float u = uniform01((unsigned long long)rng[2 * r], (unsigned long long)rng[2 * r + 1]);
+        int nn = min(a.top_k, V);
+        const float p0 = expf(sz[0] - row_max) / denom;
+        if (a.min_p > 0.f) {
+            const float thresh = p0 * a.min_p;
+            for (int i = 0; i < nn; ++i) {
+                if (expf(sz[i] - row_max) / denom < thresh) { nn = max(1, i); break; }
+            }
+        }
+        if (a.top_p < 1.0f) {
+            float cum = 0.f;
+            for (int i = 0; i < nn; ++i) {
+                cum += expf(sz[i] - row_max) / denom;
+                if (cum >= a.top_p) { nn = i + 1; break; }
+            }
+        }
+        float total = 0.f;
+        for (int i = 0; i < nn; ++i) total += expf(sz[i] - row_max) / denom;
+        const float rr = u * total;
+        float running = 0.f;
+        int pick = sid[0];
+        for (int i = 0; i < nn; ++i) {
+            running += expf(sz[i] - row_max) / denom;
+            if (rr <= running) { pick = sid[i]; break; }
+        }
+        out[r] = pick;
+        counters[r] = 0;
+    }
+}
+
 }  // namespace zlm
 
 using namespace zlm;
+
+// Floats of scratch zlm_sample_parts needs for `rows` rows (any content).  Beside it the caller keeps one int
+// counter per row that is zero before the first call; every call leaves the counters zero.
+ZLM_EXPORT long zlm_sample_parts_scratch(int rows) {
+    if (rows <= 0) return 0;
+    return (long)rows * (2 * SP_PARTS + 2 * SP_SORT);
+}
+
+// The chain for 1 <= top_k <= 64 with many blocks per row; ZLM_ERR_UNSUPPORTED for other options (the caller
+// uses zlm_sample).  Same arguments as zlm_sample, then the scratch.
+ZLM_EXPORT int zlm_sample_parts(float* logits, int rows, int V, long row_stride, float temperature, int top_k,
+                                float top_p, float min_p, float repetition_penalty, float presence_penalty,
+                                const int* history, int window, const long long* rng, int* out, int* counters,
+                                float* scratch, long scratch_floats, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (V <= 0 || row_stride < V || !(temperature > 0.f) || window < 0 || window > SP_THREADS) return ZLM_ERR_BAD_ARG;
+    const int per = (V + SP_PARTS - 1) / SP_PARTS;
+    if (top_k < 1 || top_k > SP_KMAX || per > 8192 || V < 4 * SP_PARTS) return ZLM_ERR_UNSUPPORTED;
+    if (!counters || !scratch || scratch_floats < zlm_sample_parts_scratch(rows)) return ZLM_ERR_BAD_ARG;
+    SampleArgs a;
+    a.inv_temperature = 1.0f / temperature;
+    a.top_k = top_k;
+    a.top_p = top_p;
+    a.min_p = min_p;
+    a.repetition_penalty = repetition_penalty;
+    a.presence_penalty = presence_penalty;
+    a.window = history ? window : 0;
+    float* pmax = scratch;
+    float* psum = pmax + (long)rows * SP_PARTS;
+    float* cz = psum + (long)rows * SP_PARTS;
+    int* cid = reinterpret_cast<int*>(cz + (long)rows * SP_SORT);
+    const size_t smem = sizeof(float) * (size_t)(per > 2 * SP_SORT ? per : 2 * SP_SORT);
+    sample_parts_kernel<<<dim3(SP_PARTS, rows), SP_THREADS, smem, stream>>>(logits, V, row_stride, a, history, rng, out,
+                                                                         counters, pmax, psum, cz, cid);
+    return launch_status();
+}
+
 
 ZLM_EXPORT int zlm_argmax(const float* logits, int rows, int V, long row_stride, int* out, cudaStream_t stream) {
     if (rows <= 0) return 0;

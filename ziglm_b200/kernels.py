@@ -94,6 +94,9 @@ _PROTOTYPES = {
         "zlm_gemm_tc_status": [c_void_p],
     },
     "sampling": {
+        "zlm_sample_parts_scratch": [c_int],
+        "zlm_sample_parts": [c_void_p, c_int, c_int, c_long, c_float, c_int, c_float, c_float, c_float, c_float, c_void_p,
+                             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p],
         "zlm_argmax": [c_void_p, c_int, c_int, c_long, c_void_p, c_void_p],
         "zlm_sample": [c_void_p, c_int, c_int, c_long, c_float, c_int, c_float, c_float, c_float, c_float, c_void_p,
                        c_int, c_void_p, c_void_p, c_void_p],
@@ -672,7 +675,34 @@ def sample(logits: torch.Tensor, out: torch.Tensor, rng: torch.Tensor, temperatu
         window = history.shape[1]
         if history.shape[0] < rows or window > 1024:
             raise KernelError("sample: history must be [rows, window] with window <= 1024")
+    if 1 <= top_k <= 64 and window <= 256:
+        # many blocks per row: each finds the k best of its slice, the last one to arrive cuts and draws
+        counters, scratch = _sample_scratch(logits.device, rows)
+        status = _fn("sampling", "zlm_sample_parts")(
+            logits.data_ptr(), rows, V, logits.stride(0) if rows > 1 else V, temperature, int(top_k), top_p, min_p,
+            repetition_penalty, presence_penalty, _ptr(history), window, rng.data_ptr(), out.data_ptr(),
+            counters.data_ptr(), scratch.data_ptr(), scratch.numel(), _stream())
+        if status != -2:
+            _check(status, "sample")
+            return
     _check(_fn("sampling", "zlm_sample")(
         logits.data_ptr(), rows, V, logits.stride(0) if rows > 1 else V, temperature, int(top_k), top_p, min_p,
         repetition_penalty, presence_penalty, _ptr(history), window, rng.data_ptr(), out.data_ptr(), _stream()),
         "sample")
+
+
+_SAMPLE_SCRATCH = {}
+
+
+def _sample_scratch(device: torch.device, rows: int):
+    """Counters and scratch of the many-block sampler, kept per device and grown as needed.  The counters (one
+    per row, a buffer of their own so that their place does not move with the number of rows) start at zero
+    and every call leaves them zero."""
+    counters, scratch = _SAMPLE_SCRATCH.get(device, (None, None))
+    need = int(_fn("sampling", "zlm_sample_parts_scratch")(rows))
+    if counters is None or counters.numel() < rows:
+        counters = torch.zeros(max(rows, 64), dtype=torch.int32, device=device)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(max(need, 1), dtype=torch.float32, device=device)
+    _SAMPLE_SCRATCH[device] = (counters, scratch)
+    return counters, scratch
