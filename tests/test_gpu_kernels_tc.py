@@ -55,6 +55,33 @@ def test_gemm_tc_split_k_is_exact_in_order(K, splits, T):
     assert torch.allclose(out.cpu(), base + ref_product(x, w), atol=2e-3, rtol=1e-3)
 
 
+# Steps of more than 128 tokens: the kernel that pairs two CTAs on tiles of 256 weight rows (splits=0) and the
+# one-CTA kernel (splits=1), in every output mode.  Shapes: one pair tile; an odd number of row tiles (the last
+# pair is half empty); a ragged K and N; many tiles per pair and a long K.
+@pytest.mark.parametrize("splits", [0, 1])
+@pytest.mark.parametrize("T,N,K_", [(129, 256, 64), (300, 1000, 4096), (1000, 40000, 128), (600, 392, 200),
+                                    (2050, 6144, 1024)])
+def test_gemm_tc_prompt_tiles_on_one_cta_and_on_a_pair(K, splits, T, N, K_):
+    x, w, b = rnd((T, K_), BF, seed=21), rnd((N, K_), BF, 0.05, seed=22), rnd((N,), BF, seed=23)
+    want = ref_product(x, w, b)
+    dx, dw, db = x.to(DEV), w.to(DEV), b.to(DEV)
+    for out_dtype in (BF, torch.float32):
+        out = torch.full((T, N), 7.0, dtype=out_dtype, device=DEV)
+        assert K.gemm_tc(dx, dw, out, bias=db, splits=splits)
+        tol = dict(atol=1e-3, rtol=1e-3) if out_dtype == torch.float32 else dict(atol=3e-2, rtol=2e-2)
+        assert torch.allclose(out.float().cpu(), want, **tol)
+    base = rnd((T, N), torch.float32, seed=24)
+    acc = base.to(DEV).clone()
+    assert K.gemm_tc(dx, dw, acc, bias=db, accumulate=True, splits=splits)
+    assert torch.allclose(acc.cpu(), base + want, atol=2e-3, rtol=1e-3)
+    gu = ref_product(x, w)
+    gated = torch.full((T, N // 2), 7.0, dtype=BF, device=DEV)
+    assert K.gemm_tc(dx, dw, gated, glu="silu", splits=splits)
+    torch.cuda.synchronize()
+    assert K.gemm_tc_status() == 0
+    assert torch.allclose(gated.float().cpu(), P.silu(gu[:, 0::2]) * gu[:, 1::2], atol=3e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("kind", ["silu", "gelu_tanh"])
 @pytest.mark.parametrize("T,N,K_,splits", [(8, 512, 256, 0), (45, 352, 64, 0), (100, 400, 120, 0), (8, 1024, 2048, 4),
                                            (600, 3000, 512, 0)])

@@ -108,6 +108,91 @@ __device__ __forceinline__ void grid_dependency_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// One accumulator (128 weight rows x BN tokens, in tensor memory at t_acc) to the output.  The eight epilogue
+// warps of a block call this together; sub_idx counts the sub-tiles the block has stored so far.
+template <class C, int BN, int MODE>
+__device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* tmap_y, uint32_t t_acc, int row0, int tok0,
+                                           const float* inv_s, uint8_t* stage_base, uint32_t stage_out, int& sub_idx) {
+    constexpr bool GLU = MODE == OUT_BF16_GLU || MODE == OUT_BF16_GEGLU;
+    constexpr int OUT_COLS = GLU ? TC_BM / 2 : TC_BM;              // output features of a tile
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q = warp & 3;                     // TMEM lane quarter this warp may read
+    const int egroup = (warp - 2) >> 2;         // which of the two warps of that quarter
+    const int f_local = q * 32 + lane;
+    const bool writer = !GLU || (lane & 1) == 0;
+    const int col = GLU ? f_local >> 1 : f_local;
+    const uint32_t t_lane = t_acc + ((uint32_t)(q * 32) << 16);
+
+    const int f = row0 + f_local;
+    float bias_v = 0.f;
+    if (!GLU && a.bias != nullptr && f < a.N)
+        bias_v = a.bias_dtype == ZLM_F32 ? reinterpret_cast<const float*>(a.bias)[f]
+                                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
+    const int out_f = GLU ? f >> 1 : f;
+    const int out_n = GLU ? a.N >> 1 : a.N;
+#pragma unroll 1
+    for (int c = 0; c < BN / 16; ++c) {
+        if (tok0 + c * 16 >= a.T) break;            // whole chunk beyond the last token (uniform per block)
+        const int sub_row = (c * 16) % C::SUB;       // row of this chunk inside the staged sub-tile
+        const int buf = sub_idx % C::NBUF;
+        float* stage_f = reinterpret_cast<float*>(stage_base + buf * C::SUB_BYTES);
+        __nv_bfloat16* stage_h = reinterpret_cast<__nv_bfloat16*>(stage_f);
+        if (a.tma_store && sub_row == 0 && sub_idx >= C::NBUF) {
+            // the store that last used this buffer must have read it before it is overwritten
+            if (warp == 2 && lane == 0) tma_store_wait_read_keep<C::NBUF - 1>();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+        uint32_t v[16];
+        const bool mine = (c & 1) == egroup;           // the other warp of this quarter takes the other chunks
+        if (mine) {
+            tmem_ld16(t_lane + c * 16, v);
+            tmem_ld_wait();
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (!mine) break;
+            float val = __uint_as_float(v[j]);
+            if (a.scale_ssq != nullptr) val *= inv_s[(c * 16 + j) & 63];
+            val += bias_v;
+            if (GLU) {
+                // even lanes hold a gate row, the next lane the matching up row
+                const float up = __shfl_down_sync(0xffffffffu, val, 1);
+                const float g = val;
+                val = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
+            }
+            if (a.tma_store) {
+                if (writer) {
+                    if (MODE == OUT_F32 || MODE == OUT_F32_ACC) stage_f[(sub_row + j) * OUT_COLS + col] = val;
+                    else stage_h[(sub_row + j) * OUT_COLS + col] = __float2bfloat16_rn(val);
+                }
+            } else {
+                const int tok = tok0 + c * 16 + j;
+                if (writer && tok < a.T && out_f < out_n) {
+                    if (MODE == OUT_BF16 || GLU)
+                        reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
+                    else if (MODE == OUT_F32_ACC)   // one adder per element: the order is fixed
+                        atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
+                    else
+                        reinterpret_cast<float*>(a.Y)[(long)tok * a.ldy + out_f] = val;
+                }
+            }
+        }
+        const bool last_of_sub = sub_row + 16 == C::SUB || c == BN / 16 - 1 || tok0 + (c + 1) * 16 >= a.T;
+        if (a.tma_store && last_of_sub) {
+            fence_proxy_async();                    // the staged rows become visible to the TMA engine
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (warp == 2 && lane == 0) {
+                const int x = GLU ? row0 >> 1 : row0;
+                const int y = tok0 + c * 16 - sub_row;
+                if (MODE == OUT_F32_ACC) tma_reduce_add_2d(tmap_y, stage_out + buf * C::SUB_BYTES, x, y);
+                else tma_store_2d(tmap_y, stage_out + buf * C::SUB_BYTES, x, y);
+                tma_store_commit();
+            }
+        }
+        if (a.tma_store && last_of_sub) ++sub_idx;
+    }
+}
+
 // Persistent: block b works on tiles b, b + gridDim.x, ...  The accumulator in tensor memory is
 // double-buffered, so the epilogue of one tile runs while the next tile's products are issued.
 template <int BN, int MODE, int DEEP>
@@ -362,76 +447,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             asm volatile("bar.sync 2, 256;" ::: "memory");     // the four warps go on together or not at all
             if (*abort_flag) break;
             tc_fence_after_sync();
-            const uint32_t t_lane = tmem_base + ab * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
-
-            const int f = row0 + f_local;
-            float bias_v = 0.f;
-            if (!GLU && a.bias != nullptr && f < a.N)
-                bias_v = a.bias_dtype == ZLM_F32 ? reinterpret_cast<const float*>(a.bias)[f]
-                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
-            const int out_f = GLU ? f >> 1 : f;
-            const int out_n = GLU ? a.N >> 1 : a.N;
-#pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
-                if (tok0 + c * 16 >= a.T) break;            // whole chunk beyond the last token (uniform per block)
-                const int sub_row = (c * 16) % C::SUB;       // row of this chunk inside the staged sub-tile
-                const int buf = sub_idx % C::NBUF;
-                float* stage_f = reinterpret_cast<float*>(stage_base + buf * C::SUB_BYTES);
-                __nv_bfloat16* stage_h = reinterpret_cast<__nv_bfloat16*>(stage_f);
-                if (a.tma_store && sub_row == 0 && sub_idx >= C::NBUF) {
-                    // the store that last used this buffer must have read it before it is overwritten
-                    if (warp == 2 && lane == 0) tma_store_wait_read_keep<C::NBUF - 1>();
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
-                }
-                uint32_t v[16];
-                const bool mine = (c & 1) == egroup;           // the other warp of this quarter takes the other chunks
-                if (mine) {
-                    tmem_ld16(t_lane + c * 16, v);
-                    tmem_ld_wait();
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (!mine) break;
-                    float val = __uint_as_float(v[j]);
-                    if (a.scale_ssq != nullptr) val *= inv_s[(c * 16 + j) & 63];
-                    val += bias_v;
-                    if (GLU) {
-                        // even lanes hold a gate row, the next lane the matching up row
-                        const float up = __shfl_down_sync(0xffffffffu, val, 1);
-                        const float g = val;
-                        val = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
-                    }
-                    if (a.tma_store) {
-                        if (writer) {
-                            if (MODE == OUT_F32 || MODE == OUT_F32_ACC) stage_f[(sub_row + j) * OUT_COLS + col] = val;
-                            else stage_h[(sub_row + j) * OUT_COLS + col] = __float2bfloat16_rn(val);
-                        }
-                    } else {
-                        const int tok = tok0 + c * 16 + j;
-                        if (writer && tok < a.T && out_f < out_n) {
-                            if (MODE == OUT_BF16 || GLU)
-                                reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
-                            else if (MODE == OUT_F32_ACC)   // one adder per element: the order is fixed
-                                atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
-                            else
-                                reinterpret_cast<float*>(a.Y)[(long)tok * a.ldy + out_f] = val;
-                        }
-                    }
-                }
-                const bool last_of_sub = sub_row + 16 == C::SUB || c == BN / 16 - 1 || tok0 + (c + 1) * 16 >= a.T;
-                if (a.tma_store && last_of_sub) {
-                    fence_proxy_async();                    // the staged rows become visible to the TMA engine
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
-                    if (warp == 2 && lane == 0) {
-                        const int x = GLU ? row0 >> 1 : row0;
-                        const int y = tok0 + c * 16 - sub_row;
-                        if (MODE == OUT_F32_ACC) tma_reduce_add_2d(&tmap_y, stage_out + buf * C::SUB_BYTES, x, y);
-                        else tma_store_2d(&tmap_y, stage_out + buf * C::SUB_BYTES, x, y);
-                        tma_store_commit();
-                    }
-                }
-                if (a.tma_store && last_of_sub) ++sub_idx;
-            }
+            store_tile<C, BN, MODE>(a, &tmap_y, tmem_base + ab * C::ACC_COLS, row0, tok0, inv_s, stage_base, stage_out,
+                                    sub_idx);
             // this accumulator may be overwritten by the tile after next
             tc_fence_before_sync();
             __syncwarp();
@@ -452,6 +469,194 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::COLS);
+    }
+}
+
+
+// ------------------------------------------------------------- prompts: two CTAs per tile
+// For steps of more than 128 tokens the two CTAs of a cluster work as one (tcgen05 cta_group::2) on tiles of
+// 256 weight rows x 256 tokens.  Each CTA loads its own 128 weight rows and its own 128 of the tile's tokens,
+// so a stage is 32 KB instead of 48 and the ring holds six of them for the same product; the leader (rank 0)
+// issues one instruction for both tensor cores.  Each CTA's tensor memory receives the accumulator of its own
+// 128 weight rows for all 256 tokens, and its epilogue warps write it as in the kernel above.  Barriers: the
+// stage-full barriers live in the leader and count the bytes of both CTAs' loads; stage-empty and
+// accumulator-full barriers exist in both CTAs and are signalled by one tcgen05.commit to both; the
+// accumulator-empty barriers live in the leader and collect the epilogue warps of both.
+struct PairCfg {
+    static constexpr int BN = 256;
+    static constexpr int STAGES = 6;
+    static constexpr int B_BYTES = (BN / 2) * TC_BK * 2;           // this CTA's half of the tile's tokens
+    static constexpr int ACC_COLS = BN;
+    static constexpr int COLS = 2 * BN;
+    static constexpr int SUB = sub_rows(BN);
+    static constexpr int NBUF = 2;
+    static constexpr int SUB_BYTES = SUB * TC_BM * 4;
+    static constexpr int STAGING = NBUF * SUB_BYTES;
+    static constexpr int SMEM = 1024 + STAGES * (A_BYTES + B_BYTES) + STAGING + 256;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                 const __grid_constant__ CUtensorMap tmap_y, TcArgs a) {
+    using C = PairCfg;
+    constexpr int STAGES = C::STAGES, BN = C::BN;
+    constexpr uint32_t STAGE_TX = 2u * (A_BYTES + C::B_BYTES);      // both CTAs' loads of one stage
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t a_base = base;
+    const uint32_t b_base = base + STAGES * A_BYTES;
+    const uint32_t stage_out = b_base + STAGES * C::B_BYTES;
+    const uint32_t bar_base = stage_out + C::STAGING;
+    const uint32_t full0 = bar_base, empty0 = bar_base + 8 * STAGES;
+    const uint32_t acc_full0 = bar_base + 16 * STAGES, acc_empty0 = acc_full0 + 16;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + (bar_base - base) + 16 * STAGES + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                           // 0 leads
+    const bool leader = rank == 0;
+    const int pair = (int)(blockIdx.x >> 1), n_pairs = (int)(gridDim.x >> 1);
+    const int tok_tiles = (a.T + BN - 1) / BN;
+    const int n_tiles = ((a.N + 2 * TC_BM - 1) / (2 * TC_BM)) * tok_tiles;
+    const int n_kb = a.kb_total;
+    const uint32_t lead_full0 = map_to_rank(full0, 0u);
+    const uint32_t lead_acc_empty0 = map_to_rank(acc_empty0, 0u);
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmap_w);
+        prefetch_tmap(&tmap_x);
+        if (a.tma_store) prefetch_tmap(&tmap_y);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 2 * TC_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(tmem_holder), C::COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_arrive_wait();            // both CTAs' barriers exist before either signals the other's
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+    grid_dependents_may_launch();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            const int my_rows = (int)rank * TC_BM, my_toks = (int)rank * (BN / 2);
+            int pre = 0;
+            if (pair < n_tiles) {
+                // weights do not depend on the kernel before this one
+                const int row0 = (pair / tok_tiles) * 2 * TC_BM + my_rows;
+                pre = n_kb < STAGES ? n_kb : STAGES;
+                for (int kb = 0; kb < pre; ++kb) {
+                    if (leader) mbar_expect_tx(full0 + 8 * kb, STAGE_TX);
+                    tma_load_2d_pair(a_base + kb * A_BYTES, &tmap_w, lead_full0 + 8 * kb, kb * TC_BK, row0);
+                }
+            }
+            grid_dependency_wait();
+            int it = 0;
+            bool alive = true;
+            for (int tile = pair; tile < n_tiles && alive; tile += n_pairs) {
+                const int row0 = (tile / tok_tiles) * 2 * TC_BM + my_rows;
+                const int tok0 = (tile % tok_tiles) * BN + my_toks;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= pre) {
+                        if (!mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1u, abort_flag, a.err, ERR_WAIT_EMPTY)) {
+                            alive = false;
+                            break;
+                        }
+                        if (leader) mbar_expect_tx(full0 + 8 * s, STAGE_TX);
+                        tma_load_2d_pair(a_base + s * A_BYTES, &tmap_w, lead_full0 + 8 * s, kb * TC_BK, row0);
+                    }
+                    tma_load_2d_pair(b_base + s * C::B_BYTES, &tmap_x, lead_full0 + 8 * s, kb * TC_BK, tok0);
+                }
+            }
+            if (*abort_flag && leader) {
+                // the leader's barriers count both CTAs' copies: give those in flight time to land before either
+                // CTA gives up its shared memory (the other CTA waits at the cluster barrier below)
+                const int issued = it > pre ? it : pre;
+                const int first = issued > STAGES ? issued - STAGES : 0;
+                for (int k = first; k < issued; ++k) {
+                    bool landed = false;
+                    for (uint32_t i = 0; i < WAIT_POLLS && !landed; ++i)
+                        landed = mbar_try_wait(full0 + 8 * (k % STAGES), (k / STAGES) & 1);
+                    if (!landed && a.err) atomicCAS(a.err, 0, ERR_WAIT_DRAIN);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer (the leader's)
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = idesc_bf16(2 * TC_BM, BN);
+            int it = 0, local = 0;
+            bool alive = true;
+            for (int tile = pair; tile < n_tiles && alive; tile += n_pairs, ++local) {
+                const int ab = local & 1;
+                // the epilogues of both CTAs must have emptied this accumulator (two tiles ago)
+                if (!mbar_wait(acc_empty0 + 8 * ab, ((local >> 1) & 1) ^ 1u, abort_flag, a.err, ERR_WAIT_ACCUM)) break;
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + ab * C::ACC_COLS;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full0 + 8 * s, (it / STAGES) & 1, abort_flag, a.err, ERR_WAIT_FULL)) {
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int k = 0; k < TC_BK / TC_UMMA_K; ++k) {
+                        const uint64_t da = smem_desc_sw128(a_base + s * A_BYTES + k * TC_UMMA_K * 2);
+                        const uint64_t db = smem_desc_sw128(b_base + s * C::B_BYTES + k * TC_UMMA_K * 2);
+                        umma_bf16_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty0 + 8 * s, 3);
+                }
+                if (alive) umma_commit_pair(acc_full0 + 8 * ab, 3);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- epilogue (both CTAs)
+        grid_dependency_wait();                     // the output may still be read by the kernel before this one
+        uint8_t* stage_base = smem + (stage_out - base);
+        int sub_idx = 0, local = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++local) {
+            const int row0 = (tile / tok_tiles) * 2 * TC_BM + (int)rank * TC_BM, tok0 = (tile % tok_tiles) * BN;
+            const int ab = local & 1;
+            if (n_kb > 0) mbar_wait(acc_full0 + 8 * ab, (local >> 1) & 1, abort_flag, a.err, ERR_WAIT_ACCUM);
+            asm volatile("bar.sync 2, 256;" ::: "memory");     // the eight warps go on together or not at all
+            if (*abort_flag) break;
+            tc_fence_after_sync();
+            if (row0 < a.N)                                    // an odd number of row tiles leaves the last pair half empty
+                store_tile<C, BN, MODE>(a, &tmap_y, tmem_base + ab * C::ACC_COLS, row0, tok0, nullptr, stage_base,
+                                        stage_out, sub_idx);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_acc_empty0 + 8 * ab);
+        }
+        if (a.tma_store && warp == 2 && lane == 0) tma_store_wait_read();
+        __syncwarp();
+    }
+
+    // neither CTA leaves while the other may still signal its barriers or read its shared memory
+    tc_fence_before_sync();
+    cluster_sync_arrive_wait();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, C::COLS);
     }
 }
 
@@ -587,6 +792,59 @@ static int pick_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, con
     }
 }
 
+
+// How many clusters of two can be resident at once (the SMs of a pair share a TPC); asked once.
+template <int MODE>
+static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, TcArgs a,
+                       int pair_tiles, cudaStream_t stream) {
+    using C = PairCfg;
+    static int resident = 0;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    if (resident == 0) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0, sms = 0, n = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2) sms = 148;
+        cfg.gridDim = dim3(sms & ~1);
+        cfg.numAttrs = 1;
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<MODE>, &cfg);
+        if (e != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            return ZLM_ERR_UNSUPPORTED;
+        }
+        resident = n < sms / 2 ? n : sms / 2;
+    }
+    const int pairs = pair_tiles < resident ? pair_tiles : resident;
+    a.grid_x = 2 * pairs;
+    cfg.gridDim = dim3(a.grid_x);
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE>, mw, mx, my, a);
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+static int pick_pair_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, const TcArgs& a,
+                          int pair_tiles, cudaStream_t s) {
+    switch (mode) {
+        case OUT_F32: return launch_pair<OUT_F32>(mw, mx, my, a, pair_tiles, s);
+        case OUT_F32_ACC: return launch_pair<OUT_F32_ACC>(mw, mx, my, a, pair_tiles, s);
+        case OUT_BF16_GLU: return launch_pair<OUT_BF16_GLU>(mw, mx, my, a, pair_tiles, s);
+        case OUT_BF16_GEGLU: return launch_pair<OUT_BF16_GEGLU>(mw, mx, my, a, pair_tiles, s);
+        default: return launch_pair<OUT_BF16>(mw, mx, my, a, pair_tiles, s);
+    }
+}
+
 }  // namespace zlm
 
 using namespace zlm;
@@ -594,7 +852,8 @@ using namespace zlm;
 // X: bf16 [T, K] (row stride ldx), W: bf16 [N, K] (row stride ldw), Y: float or bf16 [T, N] (row stride ldy).
 // glu: 0 = plain product; 1 / 2 = the rows of W alternate gate and up rows and Y is bf16 [T, N/2] holding
 //      silu(gate) * up (1) or tanh-gelu(gate) * up (2).
-// splits: 0 = choose, else the number of CTAs a tile's K range is split over (1..8).
+// splits: 0 = choose, else the number of CTAs a tile's K range is split over (1..8); 1 also keeps steps of more
+//      than 128 tokens on the one-CTA kernel (0 gives them to the kernel that pairs two CTAs per tile).
 // Refuses (ZLM_ERR_UNSUPPORTED) strides or addresses TMA cannot read; the caller falls back.
 //
 // An RMSNorm between two products of a step of at most 64 tokens can ride on them instead of being a kernel of
@@ -675,6 +934,15 @@ ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, 
         if (rc) return rc;
     } else {
         my = mx;                                              // never dereferenced
+    }
+    if (bn == 256 && splits == 0 && N > TC_BM && scale_ssq == nullptr) {
+        // more than 128 tokens and at least two tiles of weight rows: two CTAs per tile
+        CUtensorMap mxh;
+        rc = cached_map(&mxh, X, T, K, ldx, bn / 2);
+        if (rc) return rc;
+        const int pair_tiles = ((N + 2 * TC_BM - 1) / (2 * TC_BM)) * ((T + bn - 1) / bn);
+        rc = pick_pair_mode(mode, mw, mxh, my, a, pair_tiles, stream);
+        if (rc != ZLM_ERR_UNSUPPORTED) return rc;
     }
     switch (bn) {
         case 16: return pick_mode<16>(mode, mw, mx, my, a, stream);

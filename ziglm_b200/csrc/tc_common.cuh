@@ -233,6 +233,53 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
 // the same with B stored MN-major (bit 16)
 __host__ __device__ constexpr uint32_t idesc_bf16_b_mn(int m, int n) { return idesc_bf16(m, n) | (1u << 16); }
 
+// ------------------------------------------------------- two CTAs as one (cta_group::2)
+// The two CTAs of a cluster of two, on the SMs of one TPC, run one instruction on both tensor cores: M = 256 is
+// 128 rows of A from each CTA's shared memory, the N rows of B are split between them (N/2 each, at the same
+// shared-memory offsets), and each CTA's tensor memory receives the accumulator rows of its own 128 rows of A.
+// The even-ranked CTA issues; allocation and release of tensor memory are done by one warp of each CTA.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t holder_smem, uint32_t ncols) {  // one full warp of each CTA
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(ncols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {     // the warps that allocated
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Arrive on the barrier at this shared-memory offset in every CTA of `cta_mask` once the instructions issued so
+// far by this thread have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask) : "memory");
+}
+
+// A tile load into this CTA's shared memory whose bytes are counted on a barrier that may be the other CTA's
+// (`bar` is a shared::cluster address, see map_to_rank).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Arrive on a barrier of any CTA of the cluster (a shared::cluster address).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // ------------------------------------------------------------------ clusters
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
