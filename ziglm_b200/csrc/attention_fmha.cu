@@ -170,10 +170,14 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
+    const int b = blockIdx.y, h = blockIdx.x;
     const int tok_begin = a.cu_seqlens[b], n_new = a.cu_seqlens[b + 1] - tok_begin;
-    // the last query tiles see the most keys: give them the lowest block indices
-    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * FM_ROWS;
+    // The last query tiles see the most keys.  Blocks start in the order of their indices (x fastest), so the
+    // tile is the slowest index and counts down: the longest blocks of all heads and sequences start first and
+    // the short ones fill the SMs' last gaps (at 2,048 tokens and 32 heads the step otherwise ends 13 tile-units
+    // after it began instead of 8).  Heads are the fastest index: the heads of a kv group read the same pages
+    // at about the same time.
+    const int q0 = ((int)gridDim.z - 1 - (int)blockIdx.z) * FM_ROWS;
     if (q0 >= n_new) return;
     const int past = a.past_lens[b];
     const int kvh = h / (a.n_heads / a.n_kv);
@@ -521,7 +525,7 @@ ZLM_EXPORT int zlm_attention_prefill_fmha(const void* q, long q_row_stride, long
     if (((uintptr_t)q % 16) || (q_row_stride % 8) || ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) ||
         ((uintptr_t)out % 16))
         return ZLM_ERR_UNSUPPORTED;
-    dim3 grid((max_new + FM_ROWS - 1) / FM_ROWS, n_heads, B);
+    dim3 grid(n_heads, B, (max_new + FM_ROWS - 1) / FM_ROWS);
     if (grid.y > 65535 || grid.z > 65535) return ZLM_ERR_UNSUPPORTED;
     CUtensorMap mq, mk, mv;
     int rc = fm_map(&mq, q, total_tokens, (long)n_heads * hd, q_row_stride, FM_BQ);
