@@ -186,6 +186,17 @@ def test_attention_decode_flat(K, hd, nh, nkv, window, n_blocks):
     assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("n_blocks", [0, 3, 40])
+def test_attention_decode_flat_many_short_sequences(K, hd, n_blocks):
+    """The division among blocks counts an item's fixed work beside its pages: with many sequences of one or
+    two pages and a few long ones, blocks begin and end in that fixed part, hold many whole items, or hold
+    none of an item's pages; every page is still read once and every piece merged."""
+    lens = [3, 70, 1, 64, 127, 0, 65, 9] * 12 + [900, 2, 2, 450]
+    got, want = run_decode_flat(K, 8, 2, hd, lens, None, n_blocks, seed=31)
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
+
+
 def test_attention_decode_flat_many_tokens(K):
     """More tokens than a warp scans at once, lengths of every residue."""
     lens = [(i * 37) % 200 for i in range(70)]

@@ -371,7 +371,15 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 // (o, m, l) into slot (block + item), which grows along the walk, so blocks + items slots suffice, and
 // counts itself on the item's counter; the block that arrives last merges the pieces in slot order and
 // sets the counter back to zero.  No block waits for another.
+//
+// An item also has work that does not grow with its pages: its query rows are fetched and rotated, and its
+// result is combined over the warps, written, counted and perhaps merged.  With many short sequences that
+// work outweighs the pages, so the sequence that is divided is one of units: every item begins with
+// item_cost(HD) empty units (about what its fixed work costs, in pages) followed by one unit per page.
+// A block that holds many item starts thereby gets fewer pages.  Page k of item i is the unit
+// V_i + item_cost + k, with V_i the units before the item; block c owns the units [c * chunk, (c + 1) * chunk).
 constexpr int FLAT_MAX_TOKENS = 4096;
+template <int HD> __host__ __device__ constexpr int item_cost() { return 256 / HD; }
 
 template <int HD> using FlatCfg = AtcCfg<HD, HD == 128 ? 3 : 5>;
 
@@ -501,35 +509,44 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         }
     }
     __syncthreads();
-    const long total = (long)pre[T] * a.n_kv;
+    constexpr int IC = item_cost<HD>();
+    const long total = ((long)pre[T] + (long)IC * T) * a.n_kv;         // units: pages and the items' fixed work
     const long chunk = max(1L, (total + gridDim.x - 1) / gridDim.x);
     const long g0 = (long)blockIdx.x * chunk, g1 = min(total, g0 + chunk);
     if (g0 >= total) return;
-    // the token whose pages hold g0: the last t with n_kv * pre[t] <= g0
+    // the token whose units hold g0: the last t with n_kv * (pre[t] + IC * t) <= g0
     int t0 = 0;
     {
         int lo = 0, hi = T - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if ((long)pre[mid] * a.n_kv <= g0) lo = mid; else hi = mid - 1;
+            if (((long)pre[mid] + (long)IC * mid) * a.n_kv <= g0) lo = mid; else hi = mid - 1;
         }
         t0 = lo;
     }
     const int p0 = pre[t0 + 1] - pre[t0];
-    const int rem0 = (int)(g0 - (long)pre[t0] * a.n_kv);
-    const int kvh0 = rem0 / p0, j0 = rem0 - kvh0 * p0;
+    const int rem0 = (int)(g0 - ((long)pre[t0] + (long)IC * t0) * a.n_kv);
+    const int kvh0 = rem0 / (p0 + IC);
+    const long v0_item = g0 - (rem0 - kvh0 * (p0 + IC));               // units before the item (t0, kvh0)
 
     if (warp == ATC_CONSUMERS) {
         // ---- producer: the whole warp fetches block-table entries, lane 0 issues the copies
         // Only the page that holds a sequence's newest position was written by the kernel before this one
         // (the step's keys and values); every other page is older than the step and is requested at once.
-        int t = t0, kvh = kvh0, j = j0, issued = 0;
-        long g = g0;
+        int t = t0, kvh = kvh0, issued = 0;
+        long vi = v0_item;
         bool alive = true;
         bool waited = rope.fused && rope.store;      // the newest key and value are put in by this kernel itself
-        while (g < g1 && alive) {
+        while (vi < g1 && t < T && alive) {
             const int p_t = pre[t + 1] - pre[t];
-            const int seg = (int)min((long)(p_t - j), g1 - g);
+            // this block's pages of the item: the units [g0, g1) that fall on pages
+            const int j = (int)min((long)p_t, max(0L, g0 - vi - IC));
+            const int seg = (int)min((long)p_t, max(0L, g1 - vi - IC)) - j;
+            vi += p_t + IC;
+            if (seg <= 0) {
+                if (++kvh == a.n_kv) { kvh = 0; ++t; }
+                continue;
+            }
             const int pos = positions[t];
             const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
             const int* bt = a.block_table + (long)seq_of_token[t] * a.bt_stride + start / PAGE + j;
@@ -559,9 +576,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
                     if (!ok) { alive = false; break; }
                 }
             }
-            g += seg;
-            j += seg;
-            if (j == p_t) { j = 0; if (++kvh == a.n_kv) { kvh = 0; ++t; } }
+            if (++kvh == a.n_kv) { kvh = 0; ++t; }
         }
         if (lane == 0 && *abort_flag) {
             const int first = issued > C::STAGES ? issued - C::STAGES : 0;
@@ -581,11 +596,17 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     // a slot: [group][HD] sums, then [group][2] (maximum, denominator); slots start on 16-byte boundaries
     const long slot_floats = ((long)group * (HD + 2) + 3) / 4 * 4;
     const int half = rope.fused ? rope.rot / 2 : 0;
-    int t = t0, kvh = kvh0, j = j0, it = 0, t_angles = -1;
-    long g = g0;
-    while (g < g1) {
+    int t = t0, kvh = kvh0, it = 0, t_angles = -1;
+    long vi = v0_item;
+    for (bool first_item = true; ; first_item = false) {
+        if (!first_item && ++kvh == a.n_kv) { kvh = 0; ++t; }
+        if (vi >= g1 || t >= T) break;
         const int p_t = pre[t + 1] - pre[t];
-        const int seg = (int)min((long)(p_t - j), g1 - g);
+        const int j = (int)min((long)p_t, max(0L, g0 - vi - IC));
+        const int seg = (int)min((long)p_t, max(0L, g1 - vi - IC)) - j;
+        const long s_i = vi + IC;                                      // the unit of the item's first page
+        vi += p_t + IC;
+        if (seg <= 0) continue;
         const int pos = positions[t];
         const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
         const int first_page = start / PAGE;
@@ -672,7 +693,6 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         }
         const bool dead = bar_consumers_or(*abort_flag != 0);          // the same answer in every warp
         const int item = t * a.n_kv + kvh;
-        const long s_i = (long)pre[t] * a.n_kv + (long)kvh * p_t;        // where the item's pages begin
         const int first_block = (int)(s_i / chunk);
         const int pieces = (int)((s_i + p_t - 1) / chunk) - first_block + 1;
         __nv_bfloat16* orow = out + ((long)t * a.n_heads + (long)kvh * group) * HD;
@@ -784,9 +804,6 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         }
         bar_consumers();                           // the merge area is free for the next item
         if (dead) break;
-        g += seg;
-        j += seg;
-        if (j == p_t) { j = 0; if (++kvh == a.n_kv) { kvh = 0; ++t; } }
     }
 }
 
