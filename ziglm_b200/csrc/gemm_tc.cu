@@ -894,6 +894,8 @@ ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, 
         s = 1;
         if (bn <= 64 && tiles < 148) {
             s = (296 + tiles - 1) / tiles;                    // enough CTAs for two per SM
+            // the gated product pays for CTAs beyond one resident wave (measured at 128 tiles: 2 beats 3)
+            if (glu && s > 1 && tiles * s > 296) --s;
             if (s > 8) s = 8;
             const int most = a.kb_total / 4 > 0 ? a.kb_total / 4 : 1;   // at least 4 K blocks per CTA
             if (s > most) s = most;
