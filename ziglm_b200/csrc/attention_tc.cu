@@ -720,10 +720,10 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
             }
         }
         if (pieces > 1 && !dead) {
-            __threadfence();                       // this thread's part of the piece is visible to the GPU
-            bar_consumers();
+            bar_consumers();                       // the piece is written: thread 0 has seen every thread's part ...
             bool last = false;
             if (threadIdx.x == 0) {
+                __threadfence();                   // ... and makes it visible to the GPU before it counts the piece
                 last = atomicAdd(&counters[item], 1) == pieces - 1;
                 if (last) counters[item] = 0;      // every piece has arrived: ready for the next call
             }
@@ -732,7 +732,43 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
                 __threadfence();
                 const float* first = slots + (long)(first_block + item) * slot_floats;
                 const long step = slot_floats;
-                if (pieces <= 2 * HD) {
+                if (pieces <= 8) {
+                    // The usual case, in one round of loads and without shared memory: a thread takes four
+                    // neighbouring sums of a row and, with them, the (m, l) of that row from every piece.
+                    for (int f = threadIdx.x; f < group * HD / 4; f += ATC_CONSUMERS * 32) {
+                        const int r = f / (HD / 4);
+                        float4 v[8];
+                        float2 ml2[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            if (u < pieces) {
+                                v[u] = __ldcg(reinterpret_cast<const float4*>(first + u * step) + f);
+                                ml2[u] = __ldcg(reinterpret_cast<const float2*>(first + u * step + group * HD + 2 * r));
+                            } else {
+                                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                ml2[u] = make_float2(-INFINITY, 0.f);
+                            }
+                        }
+                        float big = -INFINITY;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) big = fmaxf(big, ml2[u].x);
+                        float den = 0.f;
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const float w = ml2[u].x == -INFINITY ? 0.f : exp2f(ml2[u].x - big);
+                            den += ml2[u].y * w;
+                            acc.x += v[u].x * w; acc.y += v[u].y * w; acc.z += v[u].z * w; acc.w += v[u].w * w;
+                        }
+                        const float inv = 1.f / den;
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+                        __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(orow + 4 * f) = packed;
+                    }
+                } else if (pieces <= 2 * HD) {
                     // (m, l) of every piece in one round of loads, turned into weights 2^(m - M) / L in place
                     float* wm = mo;                                    // [group][pieces]
                     float* wl = mo + group * pieces;
