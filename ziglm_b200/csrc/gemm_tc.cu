@@ -896,9 +896,10 @@ ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, 
             s = (296 + tiles - 1) / tiles;                    // enough CTAs for two per SM
             // the gated product pays for CTAs beyond one resident wave (measured at 128 tiles: 2 beats 3)
             if (glu && s > 1 && tiles * s > 296) --s;
-            // 64 tokens: a rank's share of the reduction over the cluster grows with the tile; a product that
-            // stores (not adds) does best with at most four ranks (measured at 48 tiles: 24.6 µs against 27.7)
-            if (bn == 64 && !accumulate && s > 4) s = 4;
+            // 32 and 64 tokens: a rank's share of the reduction over the cluster grows with the tile.  Measured
+            // inside decode steps of 32 and 64 sequences (8B shapes): a product that stores does best with five
+            // ranks (48 tiles), one that adds with seven rather than eight (32 tiles).
+            if (bn >= 32 && s > (accumulate ? 7 : 5)) s = accumulate ? 7 : 5;
             if (s > 8) s = 8;
             const int most = a.kb_total / 4 > 0 ? a.kb_total / 4 : 1;   // at least 4 K blocks per CTA
             if (s > most) s = most;
