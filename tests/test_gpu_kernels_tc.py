@@ -57,10 +57,11 @@ def test_gemm_tc_split_k_is_exact_in_order(K, splits, T):
 
 # Steps of more than 128 tokens: the kernel that pairs two CTAs on tiles of 256 weight rows (splits=0) and the
 # one-CTA kernel (splits=1), in every output mode.  Shapes: one pair tile; an odd number of row tiles (the last
-# pair is half empty); a ragged K and N; many tiles per pair and a long K.
+# pair is half empty); a ragged K and N; many tiles per pair and a long K; few tiles and a long K (the
+# accumulating product is then also cut along K: 4 and 8 parts, the last part shorter).
 @pytest.mark.parametrize("splits", [0, 1])
 @pytest.mark.parametrize("T,N,K_", [(129, 256, 64), (300, 1000, 4096), (1000, 40000, 128), (600, 392, 200),
-                                    (2050, 6144, 1024)])
+                                    (2050, 6144, 1024), (256, 4096, 14336), (200, 2048, 1000)])
 def test_gemm_tc_prompt_tiles_on_one_cta_and_on_a_pair(K, splits, T, N, K_):
     x, w, b = rnd((T, K_), BF, seed=21), rnd((N, K_), BF, 0.05, seed=22), rnd((N,), BF, seed=23)
     want = ref_product(x, w, b)

@@ -50,6 +50,7 @@ struct TcArgs {
     int kb_total;        // K blocks of 64 in all
     int kb_per_split;    // K blocks per CTA of a cluster
     int splits;
+    int ksplit;          // paired CTAs, accumulating products: parts a tile's K range is cut into (each part adds its sum)
     int grid_x;          // blocks (clusters when K is split) that share the tiles
     int tma_store;       // the output goes through shared memory and a TMA store / reduce
     int glu_kind;        // gated mode: 0 silu, 1 tanh gelu
@@ -112,7 +113,8 @@ __device__ __forceinline__ void grid_dependency_wait() {
 // warps of a block call this together; sub_idx counts the sub-tiles the block has stored so far.
 template <class C, int BN, int MODE>
 __device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* tmap_y, uint32_t t_acc, int row0, int tok0,
-                                           const float* inv_s, uint8_t* stage_base, uint32_t stage_out, int& sub_idx) {
+                                           const float* inv_s, uint8_t* stage_base, uint32_t stage_out, int& sub_idx,
+                                           bool add_bias = true) {
     constexpr bool GLU = MODE == OUT_BF16_GLU || MODE == OUT_BF16_GEGLU;
     constexpr int OUT_COLS = GLU ? TC_BM / 2 : TC_BM;              // output features of a tile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -125,7 +127,7 @@ __device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* t
 
     const int f = row0 + f_local;
     float bias_v = 0.f;
-    if (!GLU && a.bias != nullptr && f < a.N)
+    if (!GLU && a.bias != nullptr && f < a.N && add_bias)
         bias_v = a.bias_dtype == ZLM_F32 ? reinterpret_cast<const float*>(a.bias)[f]
                                         : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
     const int out_f = GLU ? f >> 1 : f;
@@ -521,7 +523,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const int pair = (int)(blockIdx.x >> 1), n_pairs = (int)(gridDim.x >> 1);
     const int tok_tiles = (a.T + BN - 1) / BN;
     const int n_tiles = ((a.N + 2 * TC_BM - 1) / (2 * TC_BM)) * tok_tiles;
-    const int n_kb = a.kb_total;
+    // A unit of work is a tile, or one of ksplit parts of its K range where the tiles alone would leave most
+    // pairs idle (accumulating products of a few hundred tokens: every part adds its sum to the output).
+    const int kb_per = (a.kb_total + a.ksplit - 1) / a.ksplit;
+    const int n_units = n_tiles * a.ksplit;
     const uint32_t lead_full0 = map_to_rank(full0, 0u);
     const uint32_t lead_acc_empty0 = map_to_rank(acc_empty0, 0u);
 
@@ -555,21 +560,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         if (lane == 0) {
             const int my_rows = (int)rank * TC_BM, my_toks = (int)rank * (BN / 2);
             int pre = 0;
-            if (pair < n_tiles) {
+            if (pair < n_units) {
                 // weights do not depend on the kernel before this one
-                const int row0 = (pair / tok_tiles) * 2 * TC_BM + my_rows;
+                const int row0 = ((pair % n_tiles) / tok_tiles) * 2 * TC_BM + my_rows;
+                const int kb_lo = (pair / n_tiles) * kb_per;
+                const int n_kb = min(kb_per, a.kb_total - kb_lo);
                 pre = n_kb < STAGES ? n_kb : STAGES;
                 for (int kb = 0; kb < pre; ++kb) {
                     if (leader) mbar_expect_tx(full0 + 8 * kb, STAGE_TX);
-                    tma_load_2d_pair(a_base + kb * A_BYTES, &tmap_w, lead_full0 + 8 * kb, kb * TC_BK, row0);
+                    tma_load_2d_pair(a_base + kb * A_BYTES, &tmap_w, lead_full0 + 8 * kb, (kb_lo + kb) * TC_BK, row0);
                 }
             }
             grid_dependency_wait();
             int it = 0;
             bool alive = true;
-            for (int tile = pair; tile < n_tiles && alive; tile += n_pairs) {
+            for (int unit = pair; unit < n_units && alive; unit += n_pairs) {
+                const int tile = unit % n_tiles;
                 const int row0 = (tile / tok_tiles) * 2 * TC_BM + my_rows;
                 const int tok0 = (tile % tok_tiles) * BN + my_toks;
+                const int kb_lo = (unit / n_tiles) * kb_per;
+                const int n_kb = min(kb_per, a.kb_total - kb_lo);
                 for (int kb = 0; kb < n_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= pre) {
@@ -578,9 +588,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
                             break;
                         }
                         if (leader) mbar_expect_tx(full0 + 8 * s, STAGE_TX);
-                        tma_load_2d_pair(a_base + s * A_BYTES, &tmap_w, lead_full0 + 8 * s, kb * TC_BK, row0);
+                        tma_load_2d_pair(a_base + s * A_BYTES, &tmap_w, lead_full0 + 8 * s, (kb_lo + kb) * TC_BK, row0);
                     }
-                    tma_load_2d_pair(b_base + s * C::B_BYTES, &tmap_x, lead_full0 + 8 * s, kb * TC_BK, tok0);
+                    tma_load_2d_pair(b_base + s * C::B_BYTES, &tmap_x, lead_full0 + 8 * s, (kb_lo + kb) * TC_BK, tok0);
                 }
             }
             if (*abort_flag && leader) {
@@ -603,9 +613,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
             constexpr uint32_t idesc = idesc_bf16(2 * TC_BM, BN);
             int it = 0, local = 0;
             bool alive = true;
-            for (int tile = pair; tile < n_tiles && alive; tile += n_pairs, ++local) {
+            for (int unit = pair; unit < n_units && alive; unit += n_pairs, ++local) {
+                const int n_kb = min(kb_per, a.kb_total - (unit / n_tiles) * kb_per);
                 const int ab = local & 1;
-                // the epilogues of both CTAs must have emptied this accumulator (two tiles ago)
+                // the epilogues of both CTAs must have emptied this accumulator (two units ago)
                 if (!mbar_wait(acc_empty0 + 8 * ab, ((local >> 1) & 1) ^ 1u, abort_flag, a.err, ERR_WAIT_ACCUM)) break;
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + ab * C::ACC_COLS;
@@ -633,16 +644,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
         grid_dependency_wait();                     // the output may still be read by the kernel before this one
         uint8_t* stage_base = smem + (stage_out - base);
         int sub_idx = 0, local = 0;
-        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++local) {
+        for (int unit = pair; unit < n_units; unit += n_pairs, ++local) {
+            const int tile = unit % n_tiles;
             const int row0 = (tile / tok_tiles) * 2 * TC_BM + (int)rank * TC_BM, tok0 = (tile % tok_tiles) * BN;
             const int ab = local & 1;
-            if (n_kb > 0) mbar_wait(acc_full0 + 8 * ab, (local >> 1) & 1, abort_flag, a.err, ERR_WAIT_ACCUM);
+            mbar_wait(acc_full0 + 8 * ab, (local >> 1) & 1, abort_flag, a.err, ERR_WAIT_ACCUM);
             asm volatile("bar.sync 2, 256;" ::: "memory");     // the eight warps go on together or not at all
             if (*abort_flag) break;
             tc_fence_after_sync();
             if (row0 < a.N)                                    // an odd number of row tiles leaves the last pair half empty
                 store_tile<C, BN, MODE>(a, &tmap_y, tmem_base + ab * C::ACC_COLS, row0, tok0, nullptr, stage_base,
-                                        stage_out, sub_idx);
+                                        stage_out, sub_idx, unit < n_tiles);      // the first part adds the bias
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(lead_acc_empty0 + 8 * ab);
@@ -826,7 +838,18 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUten
         }
         resident = n < sms / 2 ? n : sms / 2;
     }
-    const int pairs = pair_tiles < resident ? pair_tiles : resident;
+    // an accumulating product whose tiles would occupy less than half of the pairs is also cut along K
+    a.ksplit = 1;
+    if (MODE == OUT_F32_ACC && 2 * pair_tiles <= resident) {
+        int k = resident / pair_tiles;
+        if (k > 8) k = 8;
+        if (k > a.kb_total / 8) k = a.kb_total / 8;            // at least eight K blocks a part
+        if (k < 1) k = 1;
+        const int per = (a.kb_total + k - 1) / k;
+        a.ksplit = (a.kb_total + per - 1) / per;               // no empty part
+    }
+    const int units = pair_tiles * a.ksplit;
+    const int pairs = units < resident ? units : resident;
     a.grid_x = 2 * pairs;
     cfg.gridDim = dim3(a.grid_x);
     cfg.numAttrs = 2;
@@ -879,11 +902,15 @@ ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, 
     if (accumulate && y_dtype != ZLM_F32) return ZLM_ERR_BAD_ARG;
     if (glu && ((N & 1) || y_dtype != ZLM_BF16 || bias != nullptr)) return ZLM_ERR_BAD_ARG;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return ZLM_ERR_UNSUPPORTED;
-    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    // more than 64 tokens and at least two tiles of weight rows: two CTAs per tile of 256 rows x 256 tokens (with 65
+    // to 128 tokens half of the tile is empty, which costs less than leaving the K split and the second SM out)
+    const bool paired = T > 64 && splits == 0 && N > TC_BM && scale_ssq == nullptr;
+    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : (T <= 128 && !paired) ? 128 : 256;
     TcArgs a;
     a.bias = bias; a.bias_dtype = bias_dtype; a.Y = Y; a.ldy = ldy; a.T = T; a.N = N; a.K = K;
     a.kb_total = (K + TC_BK - 1) / TC_BK;
     a.glu_kind = glu == 2 ? 1 : 0;
+    a.ksplit = 1;
     a.err = error_word();
     a.norm_gain = nullptr; a.norm_gain_dtype = norm_gain_dtype; a.norm_offset = norm_offset;
     a.norm_hb = (__nv_bfloat16*)norm_hb; a.ld_hb = ld_hb; a.norm_ssq = norm_ssq; a.norm_p = (N + TC_BM - 1) / TC_BM;
@@ -941,8 +968,7 @@ ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, 
     } else {
         my = mx;                                              // never dereferenced
     }
-    if (bn == 256 && splits == 0 && N > TC_BM && scale_ssq == nullptr) {
-        // more than 128 tokens and at least two tiles of weight rows: two CTAs per tile
+    if (paired) {
         CUtensorMap mxh;
         rc = cached_map(&mxh, X, T, K, ldx, bn / 2);
         if (rc) return rc;
