@@ -292,14 +292,14 @@ def run_case(args):
     cfg = dict(LLAMA_8B)
     cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
     batch, context = args.batch, args.context
-    max_seq = context + 64
+    max_seq = max(context, args.prompt_tokens) + 64
     eng = Engine.from_config(config_from_dict(cfg), EngineOptions(
         dtype="bfloat16", max_batch=batch, max_seq_len=max_seq, max_tokens=batch * (-(-max_seq // 64) * 64), seed=1234))
     gen = torch.Generator().manual_seed(7)
     ids = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
     times = []
     if args.case == "prefill":
-        prompt = ids(PREFILL_TOKENS)
+        prompt = ids(args.prompt_tokens)
         for k in range(args.warmup + args.steps):
             slot = eng.alloc_slot()
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -311,7 +311,7 @@ def run_case(args):
             if k >= args.warmup:
                 times.append(s.elapsed_time(e))
             eng.free_slot(slot)
-        tokens = PREFILL_TOKENS
+        tokens = args.prompt_tokens
     else:
         slots = [eng.alloc_slot() for _ in range(batch)]
         # the cache is given its length without being computed: a decode step's time does not depend on its content
@@ -460,6 +460,7 @@ def main():
                          "reference-kernels: the reference's CUDA kernels alone, if they were built")
     ap.add_argument("--batch", type=int, default=8, help="--case decode: sequences in the batch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="--case decode: tokens each sequence holds")
+    ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="--case prefill: tokens of the prompt")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
