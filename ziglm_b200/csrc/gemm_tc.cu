@@ -19,6 +19,9 @@
 // their partial accumulators are summed in rank order through distributed shared
 // memory, so the result does not depend on timing and needs no scratch in global
 // memory.  Every mbarrier wait is bounded and reports through an error word.
+// Steps of more than 64 tokens run a second kernel (gemm_pair_kernel, further down) in which the two
+// CTAs of a cluster work as one on tiles of 256 weight rows x 256 tokens (tcgen05 cta_group::2); its
+// epilogue is the same code (store_tile).
 //
 // The reference multiplies with one CUDA-core GEMV per token
 // (src/cuda_bridge.cu:963-989,1439-1444); this kernel is what replaces it.
