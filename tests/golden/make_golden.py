@@ -22,7 +22,7 @@ import torch  # noqa: E402
 import helpers  # noqa: E402
 
 out = {}
-for name, seed in (("A", 101), ("B", 202)):
+for name, seed in (("A", 101), ("B", 202), ("F", 303), ("G", 404)):
     cfg = helpers.CONFIGS[name]
     tokens = helpers.random_tokens(9, cfg["vocab_size"], seed)
     with tempfile.TemporaryDirectory() as tmp:

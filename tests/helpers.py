@@ -52,15 +52,39 @@ TINY_E = {
                      "original_max_position_embeddings": 64},
     "max_position_embeddings": 512, "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "attention_bias": True,
 }
-NORM_JITTER = {"A": 0.0, "B": 0.1, "C": 0.1, "D": 0.1, "E": 0.1}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+# Two with what config.json allows beyond the usual checkpoints: biases in the feed-forward with the linear
+# stretching of positions (head size 64, so that bfloat16 takes the tensor-core kernels and the gated product
+# adds its biases in the epilogue), and the yarn stretching with every head its own key/value head.
+TINY_F = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 192, "intermediate_size": 328, "num_hidden_layers": 2,
+    "num_attention_heads": 3, "num_key_value_heads": 3, "head_dim": 64, "vocab_size": 411,
+    "rope_theta": 10000.0, "rope_scaling": {"rope_type": "linear", "factor": 4.0},
+    "max_position_embeddings": 512, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "attention_bias": False, "mlp_bias": True,
+}
+TINY_G = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 128, "intermediate_size": 136, "num_hidden_layers": 2,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 16, "vocab_size": 200,
+    "rope_theta": 10000.0,
+    "rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64,
+                     "beta_fast": 8.0, "beta_slow": 1.0},
+    "max_position_embeddings": 256, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "attention_bias": True, "mlp_bias": True,
+}
+NORM_JITTER = {"A": 0.0, "B": 0.1, "C": 0.1, "D": 0.1, "E": 0.1, "F": 0.1, "G": 0.1}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F, "G": TINY_G}
 
 
 def make_folder(tmp_path, cfg: dict, seed: int, dtype: torch.dtype, norm_jitter: float = 0.0, std: float = 0.02) -> str:
     from ziglm_b200 import config_from_dict, write_random_model
     tag = f"{cfg['hidden_size']}x{cfg['num_hidden_layers']}x{cfg['vocab_size']}"
     folder = os.path.join(str(tmp_path), f"model_{tag}_{seed}_{str(dtype).split('.')[-1]}_{norm_jitter}_{std}")
-    write_random_model(folder, config_from_dict(cfg), seed, dtype=dtype, std=std, norm_jitter=norm_jitter)
+    # the values are the same wherever they are computed; a GPU is only faster for the wide models
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    write_random_model(folder, config_from_dict(cfg), seed, dtype=dtype, std=std, norm_jitter=norm_jitter,
+                       device=device)
     return folder
 
 

@@ -59,14 +59,22 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return y
 
 
-def rope_inverse_frequencies(rot: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
-    """f_i = theta^(-2i/rot) (the reference: exp(-(2i/rot) ln base), src/model.zig:569-597), then the llama3
-    rule of the architecture's rope_scaling (the reference has none): wavelength l = 2 pi / f;
-    l < L0/high: keep; l > L0/low: f/factor; else s = (L0/l - low)/(high - low), f <- (1-s) f/factor + s f."""
+def rope_inverse_frequencies(rot: int, theta: float, scaling: Optional[dict], max_positions: int = 0) -> torch.Tensor:
+    """f_i = theta^(-2i/rot) (the reference: exp(-(2i/rot) ln base), src/model.zig:569-597), then the rule of the
+    architecture's rope_scaling (the reference has none), one frequency at a time:
+    linear: f / factor.
+    llama3: wavelength l = 2 pi / f; l < L0/high: keep; l > L0/low: f/factor; else s = (L0/l - low)/(high - low),
+            f <- (1-s) f/factor + s f.
+    yarn:   the pair that makes r rotations over L0 positions is d(r) = rot ln(L0/(2 pi r)) / (2 ln theta); between
+            lo = floor d(beta_fast) and hi = ceil d(beta_slow) (inside [0, rot-1]) the weight g rises from 0 to 1;
+            f <- (1-g) f + g f/factor."""
+    kind = None if scaling is None else scaling.get("rope_type", scaling.get("type"))
     out = []
     for i in range(rot // 2):
         f = theta ** (-(2.0 * i) / rot)
-        if scaling is not None and scaling.get("rope_type", scaling.get("type")) == "llama3":
+        if kind == "linear":
+            f = f / float(scaling["factor"])
+        elif kind == "llama3":
             factor = float(scaling["factor"])
             low = float(scaling["low_freq_factor"])
             high = float(scaling["high_freq_factor"])
@@ -79,8 +87,34 @@ def rope_inverse_frequencies(rot: int, theta: float, scaling: Optional[dict]) ->
             else:
                 s = (orig / wavelen - low) / (high - low)
                 f = (1.0 - s) * f / factor + s * f
+        elif kind == "yarn":
+            factor = float(scaling["factor"])
+            orig = float(scaling.get("original_max_position_embeddings") or max_positions)
+            lo = rot * math.log(orig / (float(scaling.get("beta_fast", 32.0)) * 2.0 * math.pi)) / (2.0 * math.log(theta))
+            hi = rot * math.log(orig / (float(scaling.get("beta_slow", 1.0)) * 2.0 * math.pi)) / (2.0 * math.log(theta))
+            if scaling.get("truncate", True):
+                lo, hi = math.floor(lo), math.ceil(hi)
+            lo, hi = max(lo, 0), min(hi, rot - 1)
+            if lo == hi:
+                hi += 0.001
+            g = min(1.0, max(0.0, (i - lo) / (hi - lo)))
+            f = (1.0 - g) * f + g * f / factor
+        elif kind not in (None, "default"):
+            raise ValueError(f"rope scaling {kind!r}")
         out.append(f)
     return torch.tensor(out, dtype=torch.float64).to(torch.float32)
+
+
+def rope_score_factor(scaling: Optional[dict]) -> float:
+    """yarn multiplies rotated queries and keys by m = attention_factor (default 0.1 ln(factor) + 1), so a score
+    grows by m * m; every other rule leaves them alone."""
+    if scaling is None or scaling.get("rope_type", scaling.get("type")) != "yarn":
+        return 1.0
+    m = scaling.get("attention_factor")
+    if m is None:
+        factor = float(scaling["factor"])
+        m = 0.1 * math.log(factor) + 1.0 if factor > 1.0 else 1.0
+    return float(m) * float(m)
 
 
 def apply_rope(x: torch.Tensor, positions: Sequence[int], inv_freq: torch.Tensor) -> torch.Tensor:
@@ -130,12 +164,14 @@ def silu(z: torch.Tensor) -> torch.Tensor:
 
 
 def swiglu(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
-           act: Optional[torch.dtype]) -> torch.Tensor:
-    """f = W_d (silu(W_g x) * (W_u x)) (src/model.zig:725-745, src/math.zig:1112-1117)."""
-    g = _round(linear(x, gate), act)
-    u = _round(linear(x, up), act)
+           act: Optional[torch.dtype], gate_bias: Optional[torch.Tensor] = None,
+           up_bias: Optional[torch.Tensor] = None, down_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """f = W_d (silu(W_g x) * (W_u x)) (src/model.zig:725-745, src/math.zig:1112-1117); the architecture's
+    mlp_bias adds a bias to each of the three products (the reference has none)."""
+    g = _round(linear(x, gate, gate_bias), act)
+    u = _round(linear(x, up, up_bias), act)
     a = _round(silu(g) * u, act)
-    return linear(a, down)
+    return linear(a, down, down_bias)
 
 
 # ----------------------------------------------------------------------- model
@@ -158,11 +194,15 @@ def decoder_layer(cfg: dict, w: Dict[str, torch.Tensor], i: int, x: torch.Tensor
     v = _round(linear(h, w[p + "self_attn.v_proj.weight"], w.get(p + "self_attn.v_proj.bias") if bias else None), act)
     q = _round(apply_rope(q.view(T, nh, hd), positions, inv_freq), act)
     k = _round(apply_rope(k.view(T, nkv, hd), positions, inv_freq), act)
-    o = attention(q, k, v.view(T, nkv, hd), 1.0 / math.sqrt(hd), cfg.get("sliding_window"))
+    scale = (1.0 / math.sqrt(hd)) * rope_score_factor(cfg.get("rope_scaling"))
+    o = attention(q, k, v.view(T, nkv, hd), scale, cfg.get("sliding_window"))
     o = _round(o.reshape(T, nh * hd), act)
     x = x + linear(o, w[p + "self_attn.o_proj.weight"], w.get(p + "self_attn.o_proj.bias") if bias else None)
     h = _round(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps), act)
-    x = x + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], act)
+    mb = cfg.get("mlp_bias", False)
+    x = x + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], act,
+                   w[p + "mlp.gate_proj.bias"] if mb else None, w[p + "mlp.up_proj.bias"] if mb else None,
+                   w[p + "mlp.down_proj.bias"] if mb else None)
     return x
 
 
@@ -171,7 +211,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
     """Logits [T, vocab] of one whole sequence: embedding, layers, final norm, head (tied to the embedding when
     there is no lm_head) (src/model.zig:495-503,543-802)."""
     hd = head_dim_of(cfg)
-    inv_freq = rope_inverse_frequencies(hd, float(cfg.get("rope_theta", 10000.0)), cfg.get("rope_scaling"))
+    inv_freq = rope_inverse_frequencies(hd, float(cfg.get("rope_theta", 10000.0)), cfg.get("rope_scaling"),
+                                        cfg.get("max_position_embeddings", 2048))
     positions = list(range(len(tokens)))
     x = embedding(tokens, w["model.embed_tokens.weight"])
     for i in range(cfg["num_hidden_layers"]):

@@ -21,7 +21,7 @@ def test_defaults_follow_the_reference():
     assert c.eos_token_ids == ()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", sorted(helpers.CONFIGS))
 def test_tiny_configs_read_and_round_trip(name):
     cfg = helpers.CONFIGS[name]
     c = config_from_dict(cfg)
@@ -44,6 +44,36 @@ def test_explicit_head_dim_and_scaling_and_eos_list():
     assert spec.layers[0].ffn.intermediate == 256 and spec.layers[0].mixer_norm.eps == 1e-6
 
 
+def test_what_config_json_allows_beyond_the_usual_checkpoints():
+    """Feed-forward biases and the stretching rules that are a transform of the frequency table."""
+    f = config_from_dict(helpers.TINY_F)
+    assert f.mlp_bias and f.rope_scaling.rope_type == "linear" and f.rope_scaling.factor == 4.0
+    layer = f.model_spec().layers[0]
+    assert layer.ffn.bias and layer.names["ffn.gate.bias"] == "mlp.gate_proj.bias"
+    assert f.rope_scaling.to_dict() == {"rope_type": "linear", "factor": 4.0}
+    g = config_from_dict(helpers.TINY_G)
+    assert g.rope_scaling.rope_type == "yarn" and g.rope_scaling.beta_fast == 8.0 and g.rope_scaling.truncate is True
+    # yarn without original_max_position_embeddings stretches from max_position_embeddings
+    cfg = copy.deepcopy(helpers.TINY_G)
+    del cfg["rope_scaling"]["original_max_position_embeddings"]
+    assert config_from_dict(cfg).rope_scaling.original_max_position_embeddings == 256
+    # older files write "type"; "default" and null mean no scaling
+    cfg["rope_scaling"] = {"type": "linear", "factor": 2.0}
+    assert config_from_dict(cfg).rope_scaling.rope_type == "linear"
+    cfg["rope_scaling"] = {"rope_type": "default"}
+    assert config_from_dict(cfg).rope_scaling is None
+
+
+def test_helpers_of_a_configuration_class_belong_to_no_architecture():
+    """Another architecture's configuration class imports its error type and typed getters from config.common."""
+    from ziglm_b200.config import common
+    assert common.ConfigError is ConfigError
+    assert common.need_int({"a": 3}, "a") == 3 and common.need_bool({}, "b", True) is True
+    assert common.token_ids({"e": [1, 2]}, "e") == (1, 2) and common.architecture_name({"architectures": ["X"]}) == "X"
+    with pytest.raises(ConfigError):
+        common.need_floats({"f": [1.0, -2.0]}, "f")
+
+
 def test_tied_head_has_no_tensor_of_its_own():
     assert config_from_dict(helpers.TINY_A).model_spec().head_name is None
 
@@ -61,7 +91,14 @@ def test_missing_required_key(key):
 @pytest.mark.parametrize("patch,word", [
     ({"hidden_size": "64"}, "hidden_size"), ({"num_hidden_layers": 0}, "num_hidden_layers"),
     ({"num_key_value_heads": 3}, "multiple"), ({"rms_norm_eps": -1.0}, "rms_norm_eps"),
-    ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "yarn"), ({"mlp_bias": True}, "mlp_bias"),
+    ({"rope_scaling": {"rope_type": "dynamic", "factor": 2.0}}, "length of the running sequence"),
+    ({"rope_scaling": {"rope_type": "longrope", "short_factor": [1.0], "long_factor": [2.0]}}, "longrope"),
+    ({"rope_scaling": {"rope_type": "ntk-by-parts", "factor": 2.0}}, "not known"),
+    ({"rope_scaling": {"rope_type": "linear"}}, "factor"),
+    ({"rope_scaling": {"rope_type": "linear", "factor": 0.5}}, "at least 1"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0, "mscale": 0.7}}, "mscale"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0, "beta_fast": 1.0, "beta_slow": 2.0}}, "beta_fast"),
+    ({"mlp_bias": "yes"}, "mlp_bias"),
     ({"hidden_act": "gelu"}, "hidden_act"), ({"tie_word_embeddings": "yes"}, "tie_word_embeddings"),
     ({"head_dim": 15}, "even"), ({"eos_token_id": "x"}, "eos_token_id"),
     ({"hidden_size": 66, "head_dim": None}, "multiple"),

@@ -126,3 +126,65 @@ def test_callback_may_end_a_request_and_echo_prompt():
     _, res, _ = run([[1, 2], [3, 4]], GenerationOptions(max_tokens=5, echo_prompt=True), callback=cb)
     assert len(res[0].tokens) == 2 + 2 and res[0].tokens[:2] == [1, 2]
     assert len(res[1].tokens) == 2 + 5
+
+
+class FaultyBackend(FakeBackend):
+    """Reports a device fault: at a given step, or when the loop asks at the end of a batch."""
+
+    def __init__(self, n_slots, fail_at_step=None, fail_at_check=False):
+        super().__init__(n_slots)
+        self.fail_at_step, self.fail_at_check, self.checks = fail_at_step, fail_at_check, 0
+
+    def step_and_sample(self, entries, requests, histories, counters, params):
+        if self.fail_at_step is not None and len(self.steps) == self.fail_at_step:
+            raise RuntimeError("a bounded wait ran out")
+        return super().step_and_sample(entries, requests, histories, counters, params)
+
+    def check(self):
+        self.checks += 1
+        if self.fail_at_check:
+            raise RuntimeError("a bounded wait ran out")
+
+
+def test_a_fault_reported_by_the_backend_ends_generation_and_gives_every_slot_back():
+    opts = GenerationOptions(max_tokens=6, ignore_eos=True, sampler=SamplerParams(greedy=True))
+    prompts = [[1, 2, 3], [4], [5, 6], [7, 8, 9, 10], [11]]
+    # in the middle of the first batch, after one request has already ended by itself
+    b = FaultyBackend(3, fail_at_step=3)
+    short = GenerationOptions(max_tokens=6, ignore_eos=True, stop_tokens=[sum([4]) % 50], sampler=SamplerParams(greedy=True))
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        run_generation(b, prompts, short, (), 3, 4096, 512, 64)
+    assert not b.held and sorted(b.free) == [0, 1, 2], "the slots of the live sequences came back, none twice"
+    assert len(b.steps) == 3
+    # the loop asks after every batch; a fault found then stops before the next batch starts
+    b = FaultyBackend(3, fail_at_check=True)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        run_generation(b, prompts, opts, (), 3, 4096, 512, 64)
+    assert b.checks == 1 and not b.held and all(len(e) <= 3 for e in b.steps)
+    # and a healthy backend is asked once per batch
+    b = FaultyBackend(3)
+    res, _ = run_generation(b, prompts, opts, (), 3, 4096, 512, 64)
+    assert b.checks == 2 and len(res) == 5
+
+
+def test_engine_check_names_the_code_and_repairs_the_counters():
+    """Engine.check_kernels with a stand-in for the device's error words (no GPU)."""
+    from ziglm_b200.engine.engine import Engine
+    from ziglm_b200.kernels import KernelError
+
+    class Buf:
+        def __init__(self): self.zeroed = []
+        def zero(self, name): self.zeroed.append(name)
+
+    class Graph:
+        def __init__(self): self.ws = Buf()
+
+    e = Engine.__new__(Engine)
+    e.ws, e._graphs, e._repeat = Buf(), {4: Graph(), 2: Graph()}, object()
+    e.check_kernels(read=lambda: {"gemm_tc": 0, "attention_tc": 0})
+    assert e._repeat is not None and e.ws.zeroed == []
+    with pytest.raises(KernelError) as err:
+        e.check_kernels(read=lambda: {"gemm_tc": 0, "attention_tc": 11})
+    assert "attention_tc" in str(err.value) and "11" in str(err.value) and "page" in str(err.value)
+    assert e._repeat is None and e.ws.zeroed == ["attn_flat_counters"]
+    assert all(g.ws.zeroed == ["attn_flat_counters"] for g in e._graphs.values())

@@ -60,6 +60,50 @@ def test_greedy_generation_matches_the_plain_implementation(models, name, dn):
     assert single.tokens == results[1].tokens
 
 
+@pytest.mark.parametrize("dn", ["float32", "bfloat16"])
+def test_a_model_made_on_the_device_holds_the_tensors_its_folder_would(tmp_path, dn):
+    """``Engine.from_config(config, seed)`` fills its weights on the device; ``write_random_model(config, seed)``
+    computes them on the host.  Both are the same function of (seed, tensor name, element), so the two engines
+    give the same logits bit for bit and the plain implementation can check a model that was never written."""
+    from ziglm_b200 import Engine, EngineOptions, config_from_dict, write_random_model
+    cfg = helpers.TINY_B
+    folder = str(tmp_path / "host_made")
+    write_random_model(folder, config_from_dict(cfg), 31, dtype=DTYPES[dn], std=0.05, norm_jitter=0.1,
+                       device=torch.device("cpu"))
+    opts = EngineOptions(dtype=dn, max_tokens=256, max_batch=2, seed=31)
+    made = Engine.from_config(cfg, opts, std=0.05, norm_jitter=0.1)
+    loaded = Engine.load(folder, opts)
+    _, w = helpers.read_folder(folder)
+    assert torch.equal(made.model.embedding.cpu(), w["model.embed_tokens.weight"])
+    assert torch.equal(made.model.final_norm.weight.cpu(), w["model.norm.weight"])
+    assert torch.equal(made.model.blocks[2].mixer.o.weight.cpu(), w["model.layers.2.self_attn.o_proj.weight"])
+    prompt = helpers.random_tokens(21, cfg["vocab_size"], 5)
+    a = made.step([(made.alloc_slot(), prompt)], [list(range(21))]).clone()
+    b = loaded.step([(loaded.alloc_slot(), prompt)], [list(range(21))]).clone()
+    assert torch.equal(a, b)
+    helpers.assert_close(a, helpers.plain_logits(folder, prompt, act=None if dn == "float32" else torch.bfloat16),
+                         DTYPES[dn], "a model made on the device against the plain model of its folder")
+
+
+def test_a_wait_that_ran_out_ends_generation_with_a_named_error_and_the_engine_recovers(models):
+    """A kernel's bounded wait is made to run out (harmlessly, by the self-test kernel) while an engine lives:
+    the engine's check raises an error that names the library and the code, and generation works afterwards."""
+    from ziglm_b200 import Engine, EngineOptions, GenerationOptions, SamplerParams, kernels
+    folder = models[("A", "bfloat16")]
+    eng = Engine.load(folder, EngineOptions(dtype="bfloat16", max_tokens=512, max_batch=3))
+    opts = GenerationOptions(max_tokens=5, ignore_eos=True, sampler=SamplerParams(greedy=True))
+    prompts = [helpers.random_tokens(n, 256, 70 + n) for n in (4, 9)]
+    before, _ = eng.generate(prompts, opts)
+    eng.check_kernels()                                    # healthy: silent
+    assert kernels.wait_selftest("gemm_tc", polls=2048) == (0, 1)
+    with pytest.raises(kernels.KernelError, match="gemm_tc: code 90"):
+        eng.generate(prompts, opts)                        # found when the first batch ends
+    eng.cache.slots.check()
+    assert eng.cache.slots.slots.n_held == 0               # the loop gave every slot back
+    after, _ = eng.generate(prompts, opts)
+    assert [r.tokens for r in after] == [r.tokens for r in before]
+
+
 def test_stop_tokens_and_model_eos(models):
     from ziglm_b200 import Engine, EngineOptions, GenerationOptions, SamplerParams
     folder = models[("B", "float32")]

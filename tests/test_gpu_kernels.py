@@ -41,6 +41,26 @@ def test_embed(K, dtype):
     assert torch.allclose(out.cpu(), P.embedding(toks.tolist(), table) * 3.0)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_random_fill_gives_the_bits_of_the_host_routine(K, dtype):
+    """Element i of a random tensor is the same on the device as in NumPy, for every i."""
+    import numpy as np
+    from ziglm_b200.weights.random_init import normal_values, random_tensor, tensor_key
+    from ziglm_b200.parts.base import ParamDecl
+    n = 3 * 1000 * 1000 + 17                        # more than the kernel's grid covers in one pass, an odd tail
+    key = tensor_key(5, "some.tensor")
+    out = torch.empty(n, dtype=dtype, device=DEV)
+    K.fill_normal(out, key, 0.25, 0.5)
+    z = np.concatenate([normal_values(key, s, min(1 << 16, n - s)) for s in range(0, n, 1 << 16)])
+    want = torch.from_numpy(np.float32(0.25) + np.float32(0.5) * z).to(dtype)
+    assert torch.equal(out.cpu(), want)
+    for decl, kw in ((ParamDecl((33, 129)), dict(std=0.3)), (ParamDecl((130,), init="ones"), dict(norm_jitter=0.1)),
+                     (ParamDecl((7,), init="ones"), {}), (ParamDecl((4, 4), kind="int"), {})):
+        a = random_tensor("model.x", decl, 9, dtype, torch.device(DEV), **kw)
+        b = random_tensor("model.x", decl, 9, dtype, torch.device("cpu"), **kw)
+        assert a.dtype == b.dtype and torch.equal(a.cpu(), b)
+
+
 @pytest.mark.parametrize("wd", DTYPES)
 @pytest.mark.parametrize("od", DTYPES)
 @pytest.mark.parametrize("d,eps", [(1000, 1e-5), (24, 1e-6), (4100, 1e-2)])

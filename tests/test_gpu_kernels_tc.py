@@ -86,13 +86,16 @@ def test_gemm_tc_prompt_tiles_on_one_cta_and_on_a_pair(K, splits, T, N, K_):
 @pytest.mark.parametrize("kind", ["silu", "gelu_tanh"])
 @pytest.mark.parametrize("T,N,K_,splits", [(8, 512, 256, 0), (45, 352, 64, 0), (100, 400, 120, 0), (8, 1024, 2048, 4),
                                            (600, 3000, 512, 0)])
-def test_gemm_tc_gated(K, kind, T, N, K_, splits):
+@pytest.mark.parametrize("bias_dtype", [None, BF, torch.float32])
+def test_gemm_tc_gated(K, kind, T, N, K_, splits, bias_dtype):
+    """act(gate + b_gate) * (up + b_up) with gate and up rows (and their biases) alternating."""
     x, w = rnd((T, K_), BF, seed=7), rnd((N, K_), BF, 0.05, seed=8)
-    gu = ref_product(x, w)
+    b = None if bias_dtype is None else rnd((N,), bias_dtype, 0.5, seed=9)
+    gu = ref_product(x, w, b)
     g, u = gu[:, 0::2], gu[:, 1::2]
     want = (P.silu(g) if kind == "silu" else torch.nn.functional.gelu(g, approximate="tanh")) * u
     out = torch.full((T, N // 2), 7.0, dtype=BF, device=DEV)
-    assert K.gemm_tc(x.to(DEV), w.to(DEV), out, glu=kind, splits=splits)
+    assert K.gemm_tc(x.to(DEV), w.to(DEV), out, bias=None if b is None else b.to(DEV), glu=kind, splits=splits)
     torch.cuda.synchronize()
     assert K.gemm_tc_status() == 0
     assert torch.allclose(out.float().cpu(), want, atol=3e-2, rtol=2e-2)
@@ -327,6 +330,33 @@ def test_tc_attention_finds_one_far_key_and_respects_the_window_edge(K, kernel, 
         want = plain_attention_rows([k], [v], q, [n - 1], [0], scale, window)
         assert torch.allclose(got, want[0], atol=3e-2, rtol=2e-2)
     assert K.attention_tc_status() == 0
+
+
+@pytest.mark.parametrize("library", ["gemm_tc", "attention_tc", "attention_fmha"])
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_library_goes_on(K, library):
+    """The give-up path of the kernels' waits, run on purpose: a block waits (4096 polls) on a barrier in its own
+    shared memory that nothing arrives on.  Nothing is in flight, nothing faults; the wait returns false, the
+    library's error word holds code 90 once, and the next real call is right."""
+    K.require((library,))
+    status = {"gemm_tc": K.gemm_tc_status, "attention_tc": K.attention_tc_status,
+              "attention_fmha": K.attention_fmha_status}[library]
+    assert status() == 0
+    passed, flag = K.wait_selftest(library, polls=4096)
+    assert passed == 0 and flag == 1                     # the wait gave up and told the other warps of its block
+    assert K.wait_errors()[library] == 90                # read through the call the engine uses ...
+    assert status() == 0                                 # ... which cleared the word
+    assert "on purpose" in K.describe_wait_errors({library: 90})
+    # the library is as usable as before
+    x = rnd((8, 256), BF, seed=1).to(DEV)
+    w = rnd((384, 256), BF, 0.05, seed=2).to(DEV)
+    out = torch.empty(8, 384, dtype=torch.float32, device=DEV)
+    assert K.gemm_tc(x, w, out)
+    assert torch.allclose(out.cpu(), ref_product(x.cpu(), w.cpu()), atol=1e-3, rtol=1e-3)
+    got, want = run_decode(K, 8, 2, 64, [5, 130, 64], None, 2)
+    assert torch.allclose(got, want, atol=2e-2, rtol=2e-2)
+    assert all(c == 0 for c in K.wait_errors().values())
+    with pytest.raises(K.KernelError):
+        K.wait_selftest("elementwise")
 
 
 def test_tc_attention_refuses_other_head_sizes(K):

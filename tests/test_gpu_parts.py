@@ -123,11 +123,13 @@ def test_attention_part_prompt_then_decode(dtype, nh, nkv, hd, d, bias, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("d,inter,act_name", [(64, 176, "silu"), (120, 200, "gelu_tanh"), (256, 1000, "silu")])
-def test_gated_mlp_part(dtype, d, inter, act_name):
+@pytest.mark.parametrize("d,inter,act_name,bias", [(64, 176, "silu", False), (120, 200, "gelu_tanh", False),
+                                                   (256, 1000, "silu", False), (192, 328, "silu", True),
+                                                   (120, 200, "gelu_tanh", True)])
+def test_gated_mlp_part(dtype, d, inter, act_name, bias):
     from ziglm_b200.config.spec import FeedForwardSpec
     from ziglm_b200.parts import feed_forward_class
-    spec = FeedForwardSpec("gated_mlp", d, inter, activation=act_name)
+    spec = FeedForwardSpec("gated_mlp", d, inter, activation=act_name, bias=bias)
     part = feed_forward_class("gated_mlp")(spec, dtype, DEV)
     w = {n: rnd(dcl.shape, dtype, 0.08, seed=20 + i) for i, (n, dcl) in enumerate(feed_forward_class("gated_mlp").declare(spec).items())}
     part.bind({n: t.to(DEV) for n, t in w.items()})
@@ -135,11 +137,12 @@ def test_gated_mlp_part(dtype, d, inter, act_name):
         h = rnd((T, d), dtype, 1.0, seed=30 + T)
         res = torch.ones(T, d, device=DEV)
         part.forward(MiniStep(dtype, [0], [T], 1, 16), h.to(DEV), res)
-        g, u = P.linear(h.float(), w["gate.weight"]), P.linear(h.float(), w["up.weight"])
+        g = P.linear(h.float(), w["gate.weight"], w.get("gate.bias"))
+        u = P.linear(h.float(), w["up.weight"], w.get("up.bias"))
         a = (P.silu(g) if act_name == "silu" else torch.nn.functional.gelu(g, approximate="tanh")) * u
         if dtype == torch.bfloat16:
             a = a.to(dtype).float()
-        want = 1.0 + P.linear(a, w["down.weight"])
+        want = 1.0 + P.linear(a, w["down.weight"], w.get("down.bias"))
         tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
         assert torch.allclose(res.cpu(), want, **tol)
 

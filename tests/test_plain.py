@@ -45,8 +45,35 @@ def test_llama3_scaling_bands():
     assert ((scaled[mid] < base[mid]) & (scaled[mid] > base[mid] / 8)).all()
 
 
+def test_linear_and_yarn_scaling_by_hand():
+    base = P.rope_inverse_frequencies(64, 10000.0, None)
+    lin = P.rope_inverse_frequencies(64, 10000.0, {"rope_type": "linear", "factor": 4.0})
+    assert torch.allclose(lin, base / 4, rtol=1e-7)
+    # yarn over 2048 original positions, 32 and 1 rotations: pair i makes 2048 f_i / (2 pi) rotations
+    sc = {"rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 2048}
+    y = P.rope_inverse_frequencies(64, 10000.0, sc)
+    rotations = 2048 * base.double() / (2 * math.pi)
+    assert torch.equal(y[rotations > 32.0 * 1.3], base[rotations > 32.0 * 1.3])        # fast pairs keep their frequency
+    assert torch.allclose(y[rotations < 1.0 / 1.3], base[rotations < 1.0 / 1.3] / 8)   # slow pairs are interpolated
+    band = (rotations < 32.0 / 1.3) & (rotations > 1.3)
+    assert band.any() and ((y[band] < base[band]) & (y[band] > base[band] / 8)).all()
+    ratio = (y / base).tolist()
+    assert all(a >= b for a, b in zip(ratio, ratio[1:]))                               # the ramp only falls
+    # the borders of the ramp: lo = floor(64 ln(2048/(64 pi)) / (2 ln 1e4)) = 8, hi = ceil(64 ln(2048/(2 pi)) / (2 ln 1e4)) = 21
+    assert ratio[8] == 1.0 and ratio[9] < 1.0 and abs(ratio[21] - 1 / 8) < 1e-7 and ratio[20] > 1 / 8 + 1e-3
+    assert abs(P.rope_score_factor(sc) - (0.1 * math.log(8.0) + 1.0) ** 2) < 1e-12
+    assert P.rope_score_factor({"rope_type": "yarn", "factor": 8.0, "attention_factor": 1.5}) == 2.25
+    assert P.rope_score_factor({"rope_type": "linear", "factor": 8.0}) == 1.0
+
+
 def test_library_frequency_table_agrees_with_the_plain_one():
-    from ziglm_b200.parts.rope import inverse_frequencies
+    from ziglm_b200.parts.rope import inverse_frequencies, score_factor
+    for sc in (helpers.TINY_F["rope_scaling"], helpers.TINY_G["rope_scaling"],
+               {"rope_type": "yarn", "factor": 8.0, "original_max_position_embeddings": 2048, "truncate": False}):
+        for rot in (16, 64, 128):
+            assert torch.allclose(inverse_frequencies(rot, 10000.0, sc), P.rope_inverse_frequencies(rot, 10000.0, sc),
+                                  rtol=2e-7, atol=0)
+        assert abs(score_factor(sc) ** 2 - P.rope_score_factor(sc)) < 1e-12
     for rot, theta, sc in ((16, 10000.0, None), (32, 500000.0, helpers.TINY_B["rope_scaling"]),
                            (128, 500000.0, {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
                                             "high_freq_factor": 4.0, "original_max_position_embeddings": 8192})):

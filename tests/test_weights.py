@@ -89,6 +89,77 @@ def test_random_folder_loads_and_is_reproducible(tmp_path, name):
     assert ("model.layers.0.self_attn.q_proj.bias" in a) == c.attention_bias
 
 
+def _normal_value_scalar(key: int, i: int):
+    """One value of the random fill, written out step by step with float32 scalars (what the library's NumPy
+    routine and its kernel compute for element i of the tensor with this key)."""
+    import math
+    import numpy as np
+    f = np.float32
+    M = (1 << 64) - 1
+    x = (key + i + 0x9E3779B97F4A7C15) & M
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & M
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & M
+    h = x ^ (x >> 31)
+    n, b = (h >> 40) + 1, (h >> 16) & 0xFFFFFF
+    e = n.bit_length() - 1
+    m = f(n) * f(2.0 ** -e)
+    if m > f(1.41421354):
+        m, e = m * f(0.5), e + 1
+    s = (m + f(-1.0)) / (m + f(1.0))
+    s2 = s * s
+    p = f(1.11111111e-1)
+    for c in (1.42857143e-1, 0.2, 3.33333333e-1, 1.0):
+        p = p * s2 + f(c)
+    ln_u = f(e - 24) * f(0.693147182) + (f(2.0) * s) * p
+    r = np.sqrt(f(-2.0) * ln_u)
+    octant, rem = b >> 21, b & 0x1FFFFF
+    xx = f((0x200000 - rem) if octant & 1 else rem) * f(3.74507039e-7)
+    x2 = xx * xx
+    if octant in (1, 2, 5, 6):
+        p = f(2.75573192e-6)
+        for c in (-1.98412698e-4, 8.33333333e-3, -1.66666667e-1, 1.0):
+            p = p * x2 + f(c)
+        c = xx * p
+    else:
+        p = f(-2.75573192e-7)
+        for c in (2.48015873e-5, -1.38888889e-3, 4.16666667e-2, -0.5, 1.0):
+            p = p * x2 + f(c)
+        c = p
+    if octant in (2, 3, 4, 5):
+        c = -c
+    z = r * c
+    # what the steps approximate: sqrt(-2 ln u1) cos(2 pi u2)
+    exact = math.sqrt(-2.0 * math.log(n / 2.0 ** 24)) * math.cos(2.0 * math.pi * b / 2.0 ** 24)
+    assert abs(float(z) - exact) < 2e-6 * max(1.0, abs(exact))
+    return z
+
+
+def test_random_values_are_a_function_of_seed_name_and_element():
+    """Any element of any tensor of a random model can be regenerated alone."""
+    import numpy as np
+    from ziglm_b200.weights.random_init import normal_values, random_tensor, tensor_key
+    from ziglm_b200.parts.base import ParamDecl
+    key = tensor_key(11, "model.layers.0.self_attn.q_proj.weight")
+    z = normal_values(key, 0, 5000)
+    assert z.dtype == np.float32 and np.isfinite(z).all()
+    for i in (0, 1, 2, 77, 4999):
+        assert _normal_value_scalar(key, i) == z[i]
+    assert np.array_equal(normal_values(key, 1234, 100), z[1234:1334])            # a slice needs no other element
+    assert not np.array_equal(normal_values(tensor_key(12, "model.layers.0.self_attn.q_proj.weight"), 0, 100), z[:100])
+    assert not np.array_equal(normal_values(tensor_key(11, "model.layers.1.self_attn.q_proj.weight"), 0, 100), z[:100])
+    big = normal_values(key, 0, 400000).astype(np.float64)
+    assert abs(big.mean()) < 0.01 and abs(big.std() - 1.0) < 0.01
+    assert abs((big ** 3).mean()) < 0.03 and abs((big ** 4).mean() - 3.0) < 0.1 and np.abs(big).max() > 4.0
+    # a tensor is mean + std * z in float32, rounded to its storage type
+    t = random_tensor("model.layers.0.self_attn.q_proj.weight", ParamDecl((50, 100)), 11, torch.bfloat16, CPU, std=0.02)
+    want = torch.from_numpy(np.float32(0.0) + np.float32(0.02) * z).to(torch.bfloat16).view(50, 100)
+    assert torch.equal(t, want)
+    n = random_tensor("model.norm.weight", ParamDecl((64,), init="ones"), 11, torch.float32, CPU, norm_jitter=0.1)
+    zn = normal_values(tensor_key(11, "model.norm.weight"), 0, 64)
+    assert torch.equal(n, torch.from_numpy(np.float32(1.0) + np.float32(0.1) * zn))
+    assert torch.equal(random_tensor("x", ParamDecl((8,), init="ones"), 1, torch.float32, CPU), torch.ones(8))
+
+
 def test_storage_types():
     assert storage_dtype("BF16", "float", torch.bfloat16) == torch.bfloat16
     assert storage_dtype("F16", "float", torch.bfloat16) == torch.bfloat16

@@ -13,7 +13,7 @@ from ctypes import c_float, c_int, c_long, c_void_p
 import pytest
 import torch
 
-from test_gpu_kernels import DEV, dense_attention_case, paged
+from test_gpu_kernels import DEV, dense_attention_case, paged, plain_attention_rows
 
 pytestmark = pytest.mark.gpu
 BF = torch.bfloat16
@@ -33,13 +33,25 @@ def entry_points():
     return fn, msg
 
 
+def wait_status():
+    """The error word of the entry point's own bounded waits (0: every wait completed), read and cleared."""
+    from ziglm_b200.csrc import load
+    status = load("attention_tc").zlm_attention_decode_noalloc_status
+    status.argtypes = [ctypes.POINTER(c_int)]
+    status.restype = c_int
+    out = c_int(-7)
+    assert status(ctypes.byref(out)) == 0
+    return out.value
+
+
 def case(nh, nkv, hd, lens_past, seed):
     ks, vs, q, positions, seq = dense_attention_case(BF, nh, nkv, hd, lens_past, [1] * len(lens_past), seed=seed)
     kp, vp, table = paged(ks, vs, 64, BF, seed=seed)
     T = q.shape[0]
     return dict(q=q.reshape(T, nh * hd).to(DEV), kp=kp.to(DEV), vp=vp.to(DEV), table=table.to(DEV),
                 pos=torch.tensor(positions, dtype=torch.int32, device=DEV),
-                seq=torch.tensor(seq, dtype=torch.int32, device=DEV), T=T)
+                seq=torch.tensor(seq, dtype=torch.int32, device=DEV), T=T,
+                plain=(ks, vs, q, positions, seq))
 
 
 def call_noalloc(fn, c, out, nh, nkv, hd, scale, window, n_splits):
@@ -54,8 +66,12 @@ def test_no_alloc_entry_point_equals_the_regular_one_twice_in_a_row(nh, nkv, hd,
     from ziglm_b200 import kernels
     fn, msg = entry_points()
     scale = 1.0 / math.sqrt(hd)
-    # two different problems one after the other: the second call finds the first one's leftovers in the scratch
-    for seed, lens_past, n_splits in ((11, [0, 130, 63, 300, 64], 3), (12, [500, 7, 129], 5)):
+    # Two different problems one after the other.  The first is large and fills much of the shared scratch; the
+    # second has fewer rows and fewer splits, so every partial result it reads lies where the first call left
+    # other values: a wrong offset into the array would read those.  The second also runs on a stream of its own.
+    side = torch.cuda.Stream()
+    for seed, lens_past, n_splits, stream in ((11, [0, 130, 63, 300, 64, 700, 5, 256], 12, None),
+                                              (12, [500, 7, 129], 2, side)):
         c = case(nh, nkv, hd, lens_past, seed)
         T = c["T"]
         want = torch.zeros(T, nh * hd, dtype=BF, device=DEV)
@@ -64,11 +80,26 @@ def test_no_alloc_entry_point_equals_the_regular_one_twice_in_a_row(nh, nkv, hd,
         assert kernels.attention_decode(c["q"], want, nh, nkv, hd, scale, window or None, c["pos"], c["seq"],
                                         c["table"], c["kp"], c["vp"], 64, n_splits, po, pm)
         got = torch.zeros_like(want)
-        rc = call_noalloc(fn, c, got, nh, nkv, hd, scale, window, n_splits)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream or torch.cuda.current_stream()):
+            rc = call_noalloc(fn, c, got, nh, nkv, hd, scale, window, n_splits)
         assert rc == 0, msg(rc).decode()
         torch.cuda.synchronize()
-        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        # against the plain statement of attention, not only against the other entry point
+        plain = plain_attention_rows(*c["plain"], scale, window or None)
+        assert torch.allclose(got.float().cpu().view(T, nh, hd), plain, atol=2e-2, rtol=2e-2)
         assert torch.equal(got, want)              # the same kernels on the same inputs
+    assert wait_status() == 0
+
+
+def test_no_alloc_entry_point_with_no_tokens_does_nothing():
+    fn, msg = entry_points()
+    c = case(4, 2, 64, [10, 20], 14)
+    out = torch.full((2, 4 * 64), 3.0, dtype=BF, device=DEV)
+    c0 = dict(c, T=0)
+    assert call_noalloc(fn, c0, out, 4, 2, 64, 0.125, 0, 2) == 0
+    torch.cuda.synchronize()
+    assert (out == 3.0).all() and wait_status() == 0
 
 
 def test_no_alloc_entry_point_refuses_what_exceeds_its_scratch():
@@ -83,3 +114,4 @@ def test_no_alloc_entry_point_refuses_what_exceeds_its_scratch():
     assert call_noalloc(fn, c, out, nh, nkv, hd, 0.1, 0, n_splits - 1) == 0
     torch.cuda.synchronize()
     assert call_noalloc(fn, c, out, nh, nkv, 48, 0.1, 0, 1) == -2
+    assert wait_status() == 0

@@ -16,76 +16,51 @@ configuration by the weight loader instead.
 """
 from __future__ import annotations
 
-import json
-import math
-import os
 from dataclasses import dataclass, asdict
 from typing import Any, Dict, Mapping, Optional, Tuple
 
+from .common import (ConfigError, architecture_name, need_bool, need_float, need_floats, need_int, read_config_json,
+                     token_ids)
 from .spec import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec,
                    PositionSpec)
 
 
-class ConfigError(ValueError):
-    """config.json is missing a key, or a value is of the wrong kind or out of range."""
-
-
-def _need_int(d: Mapping[str, Any], key: str, default: Optional[int] = None, minimum: int = 1) -> int:
-    v = d.get(key, default)
-    if v is None:
-        raise ConfigError(f"config.json: required key '{key}' is missing")
-    if isinstance(v, bool) or not isinstance(v, int):
-        raise ConfigError(f"config.json: '{key}' must be an integer, found {v!r}")
-    if v < minimum:
-        raise ConfigError(f"config.json: '{key}' must be >= {minimum}, found {v}")
-    return v
-
-
-def _need_float(d: Mapping[str, Any], key: str, default: Optional[float] = None) -> float:
-    v = d.get(key, default)
-    if v is None:
-        raise ConfigError(f"config.json: required key '{key}' is missing")
-    if isinstance(v, bool) or not isinstance(v, (int, float)):
-        raise ConfigError(f"config.json: '{key}' must be a number, found {v!r}")
-    v = float(v)
-    if not math.isfinite(v) or v <= 0.0:
-        raise ConfigError(f"config.json: '{key}' must be a positive finite number, found {v}")
-    return v
-
-
-def _need_bool(d: Mapping[str, Any], key: str, default: bool) -> bool:
-    v = d.get(key, default)
-    if v is None:
-        return default
-    if not isinstance(v, bool):
-        raise ConfigError(f"config.json: '{key}' must be true or false, found {v!r}")
-    return v
-
-
-def _token_ids(d: Mapping[str, Any], key: str) -> Tuple[int, ...]:
-    v = d.get(key)
-    if v is None:
-        return ()
-    items = v if isinstance(v, (list, tuple)) else [v]
-    out = []
-    for t in items:
-        if isinstance(t, bool) or not isinstance(t, int) or t < 0:
-            raise ConfigError(f"config.json: '{key}' must be a token id or a list of them, found {v!r}")
-        out.append(t)
-    return tuple(out)
+_REFUSED_SCALINGS = {
+    "dynamic": "its frequencies depend on the length of the running sequence, so keys already in the cache "
+               "would have been rotated with another table than the queries that read them",
+    "longrope": "it switches between two tables of factors by the length of the running sequence, so keys already "
+                "in the cache would have been rotated with another table than the queries that read them",
+}
 
 
 @dataclass(frozen=True)
 class RopeScaling:
-    """``rope_scaling`` of kind "llama3": low frequencies are slowed by ``factor``."""
+    """``rope_scaling`` of config.json: how the table of rotary frequencies is stretched for long contexts.
+
+    ``rope_type`` (older files: ``type``) selects the rule; every rule is a transform of the table, applied
+    once when the model is built (the formulas are in ``ziglm_b200/parts/rope.py``):
+      "linear"  every frequency is divided by ``factor``;
+      "llama3"  low frequencies are divided by ``factor``, high ones stay, those between are blended;
+                needs ``low_freq_factor``, ``high_freq_factor``, ``original_max_position_embeddings``;
+      "yarn"    frequencies below a band are divided by ``factor``, those above stay, with a linear ramp over
+                the band given by ``beta_fast`` (32) and ``beta_slow`` (1) rotations over
+                ``original_max_position_embeddings`` (default: max_position_embeddings); queries and keys are
+                scaled by ``attention_factor`` (default 0.1 ln(factor) + 1).
+    Rules whose table changes with the length of the running sequence ("dynamic", "longrope") are refused.
+    The reference knows no rope_scaling at all (src/safetensors.zig:548-591 never reads the key).
+    """
     rope_type: str
     factor: float
-    low_freq_factor: float
-    high_freq_factor: float
-    original_max_position_embeddings: int
+    low_freq_factor: Optional[float] = None
+    high_freq_factor: Optional[float] = None
+    original_max_position_embeddings: Optional[int] = None
+    beta_fast: Optional[float] = None
+    beta_slow: Optional[float] = None
+    attention_factor: Optional[float] = None
+    truncate: Optional[bool] = None
 
     @classmethod
-    def from_dict(cls, d: Optional[Mapping[str, Any]]) -> Optional["RopeScaling"]:
+    def from_dict(cls, d: Optional[Mapping[str, Any]], max_positions: Optional[int] = None) -> Optional["RopeScaling"]:
         if d is None:
             return None
         if not isinstance(d, Mapping):
@@ -93,21 +68,45 @@ class RopeScaling:
         kind = d.get("rope_type", d.get("type"))
         if kind in (None, "default"):
             return None
-        if kind != "llama3":
-            raise ConfigError(f"config.json: rope_scaling of type {kind!r} is not supported (only 'llama3')")
-        s = cls(
-            rope_type="llama3",
-            factor=_need_float(d, "factor"),
-            low_freq_factor=_need_float(d, "low_freq_factor"),
-            high_freq_factor=_need_float(d, "high_freq_factor"),
-            original_max_position_embeddings=_need_int(d, "original_max_position_embeddings"),
-        )
-        if s.high_freq_factor <= s.low_freq_factor:
-            raise ConfigError("config.json: rope_scaling.high_freq_factor must exceed low_freq_factor")
+        if kind in _REFUSED_SCALINGS:
+            raise ConfigError(f"config.json: rope_scaling of type {kind!r} is not supported: {_REFUSED_SCALINGS[kind]}")
+        if kind == "linear":
+            s = cls(rope_type="linear", factor=need_float(d, "factor"))
+        elif kind == "llama3":
+            s = cls(
+                rope_type="llama3",
+                factor=need_float(d, "factor"),
+                low_freq_factor=need_float(d, "low_freq_factor"),
+                high_freq_factor=need_float(d, "high_freq_factor"),
+                original_max_position_embeddings=need_int(d, "original_max_position_embeddings"),
+            )
+            if s.high_freq_factor <= s.low_freq_factor:
+                raise ConfigError("config.json: rope_scaling.high_freq_factor must exceed low_freq_factor")
+        elif kind == "yarn":
+            for key in ("mscale", "mscale_all_dim"):
+                if d.get(key) is not None:
+                    raise ConfigError(f"config.json: rope_scaling.{key} (a variant of yarn for another architecture) "
+                                      "is not supported")
+            s = cls(
+                rope_type="yarn",
+                factor=need_float(d, "factor"),
+                original_max_position_embeddings=need_int(d, "original_max_position_embeddings", default=max_positions),
+                beta_fast=need_float(d, "beta_fast", default=32.0),
+                beta_slow=need_float(d, "beta_slow", default=1.0),
+                attention_factor=need_float(d, "attention_factor") if d.get("attention_factor") is not None else None,
+                truncate=need_bool(d, "truncate", True),
+            )
+            if s.beta_fast <= s.beta_slow:
+                raise ConfigError("config.json: rope_scaling.beta_fast must exceed beta_slow")
+        else:
+            raise ConfigError(f"config.json: rope_scaling of type {kind!r} is not known "
+                              "(default, linear, llama3, yarn)")
+        if s.factor < 1.0:
+            raise ConfigError(f"config.json: rope_scaling.factor must be at least 1, found {s.factor}")
         return s
 
     def to_dict(self) -> Dict[str, Any]:
-        return asdict(self)
+        return {k: v for k, v in asdict(self).items() if v is not None}
 
 
 @dataclass(frozen=True)
@@ -138,12 +137,10 @@ class LlamaConfig:
     def from_dict(cls, d: Mapping[str, Any]) -> "LlamaConfig":
         if not isinstance(d, Mapping):
             raise ConfigError("config.json must hold a JSON object")
-        arch = d.get("architectures")
-        if not (isinstance(arch, (list, tuple)) and arch and isinstance(arch[0], str)):
-            raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
-        hidden = _need_int(d, "hidden_size")
-        heads = _need_int(d, "num_attention_heads")
-        kv_heads = _need_int(d, "num_key_value_heads", default=heads)
+        arch = architecture_name(d)
+        hidden = need_int(d, "hidden_size")
+        heads = need_int(d, "num_attention_heads")
+        kv_heads = need_int(d, "num_key_value_heads", default=heads)
         if d.get("head_dim") is None:
             if hidden % heads:
                 raise ConfigError(
@@ -151,7 +148,7 @@ class LlamaConfig:
                     "and no head_dim is given")
             head_dim = hidden // heads
         else:
-            head_dim = _need_int(d, "head_dim")
+            head_dim = need_int(d, "head_dim")
         if heads % kv_heads:
             raise ConfigError(
                 f"config.json: num_attention_heads {heads} is not a multiple of num_key_value_heads {kv_heads}")
@@ -164,27 +161,25 @@ class LlamaConfig:
         if bos is not None and (isinstance(bos, bool) or not isinstance(bos, int)):
             raise ConfigError(f"config.json: 'bos_token_id' must be an integer, found {bos!r}")
         cfg = cls(
-            architecture=arch[0],
+            architecture=arch,
             hidden_size=hidden,
-            intermediate_size=_need_int(d, "intermediate_size"),
-            num_hidden_layers=_need_int(d, "num_hidden_layers"),
+            intermediate_size=need_int(d, "intermediate_size"),
+            num_hidden_layers=need_int(d, "num_hidden_layers"),
             num_attention_heads=heads,
             num_key_value_heads=kv_heads,
             head_dim=head_dim,
-            vocab_size=_need_int(d, "vocab_size"),
-            rms_norm_eps=_need_float(d, "rms_norm_eps", default=1e-5),
-            rope_theta=_need_float(d, "rope_theta", default=10000.0),
-            rope_scaling=RopeScaling.from_dict(d.get("rope_scaling")),
-            max_position_embeddings=_need_int(d, "max_position_embeddings", default=2048),
-            tie_word_embeddings=_need_bool(d, "tie_word_embeddings", False),
-            attention_bias=_need_bool(d, "attention_bias", False),
-            mlp_bias=_need_bool(d, "mlp_bias", False),
+            vocab_size=need_int(d, "vocab_size"),
+            rms_norm_eps=need_float(d, "rms_norm_eps", default=1e-5),
+            rope_theta=need_float(d, "rope_theta", default=10000.0),
+            rope_scaling=RopeScaling.from_dict(d.get("rope_scaling"), need_int(d, "max_position_embeddings", default=2048)),
+            max_position_embeddings=need_int(d, "max_position_embeddings", default=2048),
+            tie_word_embeddings=need_bool(d, "tie_word_embeddings", False),
+            attention_bias=need_bool(d, "attention_bias", False),
+            mlp_bias=need_bool(d, "mlp_bias", False),
             hidden_act="silu",
             bos_token_id=bos,
-            eos_token_ids=_token_ids(d, "eos_token_id"),
+            eos_token_ids=token_ids(d, "eos_token_id"),
         )
-        if cfg.mlp_bias:
-            raise ConfigError("config.json: mlp_bias true is not supported")
         return cfg
 
     @classmethod
@@ -239,7 +234,7 @@ class LlamaConfig:
                                 position=position),
                 ffn_norm=NormSpec("rmsnorm", d, self.rms_norm_eps),
                 ffn=FeedForwardSpec(kind="gated_mlp", width=d, intermediate=self.intermediate_size,
-                                    activation="silu", bias=False),
+                                    activation="silu", bias=self.mlp_bias),
                 names={
                     "mixer_norm.weight": "input_layernorm.weight",
                     "mixer.q.weight": "self_attn.q_proj.weight",
@@ -254,6 +249,9 @@ class LlamaConfig:
                     "ffn.gate.weight": "mlp.gate_proj.weight",
                     "ffn.up.weight": "mlp.up_proj.weight",
                     "ffn.down.weight": "mlp.down_proj.weight",
+                    "ffn.gate.bias": "mlp.gate_proj.bias",
+                    "ffn.up.bias": "mlp.up_proj.bias",
+                    "ffn.down.bias": "mlp.down_proj.bias",
                 },
             ))
         return ModelSpec(
@@ -279,21 +277,10 @@ class LlamaConfig:
         per_layer = d * q + 2 * d * kv + q * d + 3 * d * i + 2 * d
         if self.attention_bias:
             per_layer += q + 2 * kv + d
+        if self.mlp_bias:
+            per_layer += 2 * i + d
         total = self.num_hidden_layers * per_layer + v * d + d
         if not self.tie_word_embeddings:
             total += v * d
         return total
 
-
-def read_config_json(folder: str) -> Dict[str, Any]:
-    path = os.path.join(folder, "config.json")
-    try:
-        with open(path, "r", encoding="utf-8") as f:
-            d = json.load(f)
-    except FileNotFoundError:
-        raise ConfigError(f"{path} does not exist") from None
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"{path} is not valid JSON: {e}") from None
-    if not isinstance(d, dict):
-        raise ConfigError(f"{path} must hold a JSON object")
-    return d

@@ -12,7 +12,8 @@ import json
 import os
 from typing import Any, Callable, Dict, Mapping
 
-from .llama import ConfigError, LlamaConfig, read_config_json
+from .common import ConfigError, architecture_name, read_config_json
+from .llama import LlamaConfig
 from .spec import ModelSpec
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -34,13 +35,11 @@ def registered_architectures():
 
 
 def config_from_dict(d: Mapping[str, Any]):
-    arch = d.get("architectures") if isinstance(d, Mapping) else None
-    if not (isinstance(arch, (list, tuple)) and arch and isinstance(arch[0], str)):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
-    cls = _ARCHITECTURES.get(arch[0])
+    arch = architecture_name(d)
+    cls = _ARCHITECTURES.get(arch)
     if cls is None:
         raise ConfigError(
-            f"architecture {arch[0]!r} is not registered (known: {', '.join(registered_architectures())})")
+            f"architecture {arch!r} is not registered (known: {', '.join(registered_architectures())})")
     return cls.from_dict(d)
 
 

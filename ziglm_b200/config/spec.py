@@ -70,7 +70,11 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One set of layer weights and how its parts are arranged."""
+    """One set of layer weights and how its parts are arranged.
+
+    ``options`` carries what an arrangement other than the pre-norm one needs beyond the four parts: further
+    part specs (a norm after the mixer, say) or scalars, under names the arrangement defines.  The pre-norm
+    arrangement reads none."""
     block: str                     # registry key of the arrangement, e.g. "prenorm"
     prefix: str                    # tensor-name prefix of this layer's weights
     mixer_norm: NormSpec
@@ -78,6 +82,17 @@ class LayerSpec:
     ffn_norm: NormSpec
     ffn: FeedForwardSpec
     # local parameter name (as the part declares it) -> name under ``prefix``
+    names: Mapping[str, str] = field(default_factory=dict)
+    options: Mapping[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class HookSpec:
+    """A part that runs once per step outside the layers: on the embedded tokens before the first layer
+    (learned absolute positions, an embedding norm) or on the logits after the head (a bias, a soft cap)."""
+    kind: str                      # registry key
+    options: Mapping[str, Any] = field(default_factory=dict)
+    # local parameter name (as the part declares it) -> full tensor name in the weight files
     names: Mapping[str, str] = field(default_factory=dict)
 
 
@@ -95,6 +110,9 @@ class ModelSpec:
     embedding_scale: float = 1.0
     max_positions: int = 0
     stop_token_ids: Tuple[int, ...] = ()
+    embed_hook: Optional[HookSpec] = None      # runs on the float32 residual [T, width] after the embedding
+    logits_hook: Optional[HookSpec] = None     # runs on the float32 logits [n_want, vocab] after the head
+    options: Mapping[str, Any] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
         for i in self.schedule:

@@ -556,3 +556,9 @@ ZLM_EXPORT int zlm_attention_fmha_status(int* out) {
     if (*out != 0) cudaMemset(w, 0, sizeof(int));
     return 0;
 }
+
+// Runs the give-up path of the bounded waits once, harmlessly (see wait_selftest_kernel): afterwards
+// zlm_attention_fmha_status returns 90.  seen: two ints on the device.
+ZLM_EXPORT int zlm_attention_fmha_wait_selftest(int polls, int* seen, cudaStream_t stream) {
+    return tc::run_wait_selftest(fm_error_word(), polls, seen, stream);
+}

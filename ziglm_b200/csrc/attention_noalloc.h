@@ -15,7 +15,8 @@
  * process exits).  A larger request is refused with ZLM_NOALLOC_ERR_TOO_LARGE and nothing is launched.
  *
  * Set-up: the first call on a device (with that device current) looks up the device address of the scratch
- * once and keeps it.  Make that first call outside any stream capture.
+ * once and keeps it, and raises the kernel's shared-memory limit once per head size.  Make the first call
+ * for each head size outside any stream capture.
  *
  * Sharing: every call on a device uses the same array, which keeps what the last call left.  Nothing in it
  * has to start at zero (every element the merge reads is written earlier in the same call), but two calls
@@ -46,7 +47,14 @@ int zlm_attention_decode_noalloc(const void* q, long q_row_stride, void* out, in
                                  const void* v_pages, long n_pages, int page_size, int n_splits,
                                  cudaStream_t stream);
 
-/* A sentence for a code returned by the function above. */
+/* The bounded waits of the kernels behind the function above report through an error word of their own (not
+ * the one zlm_attention_tc_status reads).  This reads it into *out (0: every wait completed; 11: a cache page
+ * never landed; 12: a stage never drained; 4: copies were still in flight when a block gave up) and clears it.
+ * A non-zero code means the output of some call since the last check is not valid.  Allocates nothing;
+ * waits for the device.  Returns 0 or a cudaError_t. */
+int zlm_attention_decode_noalloc_status(int* out);
+
+/* A sentence for a code returned by zlm_attention_decode_noalloc. */
 const char* zlm_attention_decode_noalloc_error(int code);
 
 #ifdef __cplusplus

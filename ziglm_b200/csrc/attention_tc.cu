@@ -1224,6 +1224,12 @@ ZLM_EXPORT int zlm_attention_tc_status(int* out) {
     return 0;
 }
 
+// Runs the give-up path of the bounded waits once, harmlessly (see wait_selftest_kernel): afterwards
+// zlm_attention_tc_status returns 90.  seen: two ints on the device.
+ZLM_EXPORT int zlm_attention_tc_wait_selftest(int polls, int* seen, cudaStream_t stream) {
+    return tc::run_wait_selftest(att_error_word(), polls, seen, stream);
+}
+
 // ------------------------------------------------- decode attention that allocates nothing
 // See attention_noalloc.h: the same kernels as zlm_attention_decode, with the split scratch and the
 // error word in file-scope device arrays instead of memory the caller (or this library) allocates.
@@ -1236,6 +1242,7 @@ static __device__ __align__(256) int g_noalloc_err[64];
 
 struct NoAllocDevice {
     bool ready;
+    bool smem_set[2];       // the shared-memory limit of the kernel for head size 64 / 128 has been raised
     float* scratch;
     int* err;
 };
@@ -1244,7 +1251,7 @@ static std::mutex g_noalloc_mu;
 
 // In host code the arrays' names are stand-ins, not device addresses: the address that kernels may use
 // comes from cudaGetSymbolAddress, asked once per device with that device current.
-static int noalloc_setup(float** scratch, int** err) {
+static int noalloc_setup(float** scratch, int** err, int hd = 0) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
@@ -1260,6 +1267,16 @@ static int noalloc_setup(float** scratch, int** err) {
         if (e != cudaSuccess) return (int)e;
         d.err = static_cast<int*>(p);
         d.ready = true;
+    }
+    if (hd == 64 && !d.smem_set[0]) {
+        e = cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<64>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        d.smem_set[0] = true;
+    }
+    if (hd == 128 && !d.smem_set[1]) {
+        e = cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<128>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        d.smem_set[1] = true;
     }
     *scratch = d.scratch;
     *err = d.err;
@@ -1284,7 +1301,7 @@ ZLM_EXPORT int zlm_attention_decode_noalloc(const void* q, long q_row_stride, vo
     if (rows * (hd + 2) > (long)ZLM_NOALLOC_SCRATCH_FLOATS) return ZLM_NOALLOC_ERR_TOO_LARGE;
     float* scratch = nullptr;
     int* err = nullptr;
-    int rc = noalloc_setup(&scratch, &err);
+    int rc = noalloc_setup(&scratch, &err, hd);
     if (rc) return rc;
     float* part_o = scratch;                       // [rows, hd]
     float* part_ml = scratch + rows * hd;          // [rows, 2]
@@ -1305,21 +1322,29 @@ ZLM_EXPORT int zlm_attention_decode_noalloc(const void* q, long q_row_stride, vo
     a.err = err;
     dim3 grid(n_splits, n_kv, T);
     if (hd == 128) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             DecodeCfg<128>::SMEM);
-        if (e != cudaSuccess) return (int)e;
         attn_decode_kernel<128><<<grid, ATC_THREADS, DecodeCfg<128>::SMEM, stream>>>(mk, mv, a, positions,
                                                                                      seq_of_token, part_o, part_ml);
         attn_merge_kernel<128><<<T * n_heads, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits);
     } else {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             DecodeCfg<64>::SMEM);
-        if (e != cudaSuccess) return (int)e;
         attn_decode_kernel<64><<<grid, ATC_THREADS, DecodeCfg<64>::SMEM, stream>>>(mk, mv, a, positions, seq_of_token,
                                                                                    part_o, part_ml);
         attn_merge_kernel<64><<<T * n_heads, 64, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_splits);
     }
     return launch_status();
+}
+
+// The error word of this entry point's bounded waits (its own, in the library's device memory): *out receives
+// 0 or the code of a wait that ran out since the last call, and the word is cleared.  Allocates nothing;
+// synchronises the device.
+ZLM_EXPORT int zlm_attention_decode_noalloc_status(int* out) {
+    float* scratch = nullptr;
+    int* err = nullptr;
+    int rc = noalloc_setup(&scratch, &err);
+    if (rc) return rc;
+    cudaError_t e = cudaMemcpy(out, err, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return (int)e;
+    if (*out != 0) e = cudaMemset(err, 0, sizeof(int));
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 ZLM_EXPORT const char* zlm_attention_decode_noalloc_error(int code) {

@@ -153,6 +153,11 @@ def build(names: Optional[Iterable[str]] = None, jobs: Optional[int] = None) -> 
         return list(pool.map(_compile, todo))
 
 
+def is_loaded(name: str) -> bool:
+    with _lock:
+        return name in _loaded
+
+
 def load(name: str) -> ctypes.CDLL:
     """The shared library of ``<name>.cu``, compiled first if need be."""
     with _lock:

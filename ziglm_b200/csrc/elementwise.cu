@@ -154,6 +154,87 @@ static int norm_threads(int d) {
     return t;
 }
 
+
+// -------------------------------------------------------------- random weights
+// Element i of a tensor with key k is a function of (k, i) alone:
+//   h = mix64(k + i); a = top 24 bits of h, b = the 24 bits below them;
+//   u1 = (a + 1) / 2^24 in (0, 1], angle = 2 pi b / 2^24;
+//   z = sqrt(-2 ln u1) * cos(angle)                      (Box-Muller, one of its two values)
+//   value = mean + std * z, rounded to the storage type.
+// Every floating operation is a single IEEE-rounded +, *, / or sqrt in float (the _rn intrinsics keep
+// the compiler from fusing them), and ln, sin and cos are the short polynomials below, so the same
+// steps in NumPy give the same bits (ziglm_b200/weights/random_init.py: normal_values).  The
+// reference fills its fixtures from one sequential generator (src/synthetic.zig:232-249); a counter
+// lets any element be regenerated without the others, on the host or on the device.
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__device__ __forceinline__ float det_sin(float x) {          // x in [0, pi/4]
+    const float x2 = __fmul_rn(x, x);
+    float p = 2.75573192e-6f;                                 // 1/9!
+    p = __fadd_rn(__fmul_rn(p, x2), -1.98412698e-4f);         // -1/7!
+    p = __fadd_rn(__fmul_rn(p, x2), 8.33333333e-3f);          // 1/5!
+    p = __fadd_rn(__fmul_rn(p, x2), -1.66666667e-1f);         // -1/3!
+    p = __fadd_rn(__fmul_rn(p, x2), 1.0f);
+    return __fmul_rn(x, p);
+}
+
+__device__ __forceinline__ float det_cos(float x) {          // x in [0, pi/4]
+    const float x2 = __fmul_rn(x, x);
+    float p = -2.75573192e-7f;                                // -1/10!
+    p = __fadd_rn(__fmul_rn(p, x2), 2.48015873e-5f);          // 1/8!
+    p = __fadd_rn(__fmul_rn(p, x2), -1.38888889e-3f);         // -1/6!
+    p = __fadd_rn(__fmul_rn(p, x2), 4.16666667e-2f);          // 1/4!
+    p = __fadd_rn(__fmul_rn(p, x2), -0.5f);
+    return __fadd_rn(__fmul_rn(p, x2), 1.0f);
+}
+
+__device__ __forceinline__ float det_normal(uint64_t key, uint64_t index) {
+    const uint64_t h = mix64(key + index);
+    const uint32_t n = (uint32_t)(h >> 40) + 1u;              // 1 .. 2^24
+    const uint32_t b = (uint32_t)(h >> 16) & 0xFFFFFFu;
+    // ln(n / 2^24) = (e - 24) ln 2 + ln m with n = m 2^e, m in (sqrt(1/2), sqrt(2)]
+    int e = 31 - __clz(n);
+    float m = __fmul_rn((float)n, __int_as_float((127 - e) << 23));      // exact: n < 2^25, a power of two
+    if (m > 1.41421354f) { m = __fmul_rn(m, 0.5f); e += 1; }
+    const float s = __fdiv_rn(__fadd_rn(m, -1.0f), __fadd_rn(m, 1.0f));
+    const float s2 = __fmul_rn(s, s);
+    float p = 1.11111111e-1f;                                 // 1/9
+    p = __fadd_rn(__fmul_rn(p, s2), 1.42857143e-1f);          // 1/7
+    p = __fadd_rn(__fmul_rn(p, s2), 0.2f);
+    p = __fadd_rn(__fmul_rn(p, s2), 3.33333333e-1f);
+    p = __fadd_rn(__fmul_rn(p, s2), 1.0f);
+    const float ln_m = __fmul_rn(__fmul_rn(2.0f, s), p);
+    const float ln_u = __fadd_rn(__fmul_rn((float)(e - 24), 0.693147182f), ln_m);
+    const float r = __fsqrt_rn(__fmul_rn(-2.0f, ln_u));
+    // cos(2 pi b / 2^24) by octants, the argument folded into [0, pi/4]
+    const uint32_t oct = b >> 21, rem = b & 0x1FFFFFu;
+    const float step = 3.74507039e-7f;                        // 2 pi / 2^24
+    const float x = __fmul_rn((float)((oct & 1u) ? 0x200000u - rem : rem), step);
+    float c;
+    switch (oct) {
+        case 0: c = det_cos(x); break;
+        case 1: c = det_sin(x); break;
+        case 2: c = -det_sin(x); break;
+        case 3: c = -det_cos(x); break;
+        case 4: c = -det_cos(x); break;
+        case 5: c = -det_sin(x); break;
+        case 6: c = det_sin(x); break;
+        default: c = det_cos(x); break;
+    }
+    return __fmul_rn(r, c);
+}
+
+template <typename TO>
+__global__ void fill_normal_kernel(TO* __restrict__ out, long n, uint64_t key, float mean, float std_dev) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+        out[i] = from_float<TO>(__fadd_rn(mean, __fmul_rn(std_dev, det_normal(key, (uint64_t)i))));
+}
+
 }  // namespace zlm
 
 using namespace zlm;
@@ -227,6 +308,22 @@ ZLM_EXPORT int zlm_convert(const void* in, int in_dtype, void* out, int out_dtyp
         convert_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float*)in, (__nv_bfloat16*)out, n);
     else if (in_dtype == ZLM_BF16 && out_dtype == ZLM_F32)
         convert_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (float*)out, n);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return launch_status();
+}
+
+// out[i] = mean + std * z(key, i), i < n, z a standard normal value that depends on (key, i) only.
+ZLM_EXPORT int zlm_fill_normal(void* out, int out_dtype, long n, unsigned long long key, float mean, float std_dev,
+                               cudaStream_t stream) {
+    if (n < 0 || (n > 0 && !out)) return ZLM_ERR_BAD_ARG;
+    if (n == 0) return 0;
+    long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_dtype == ZLM_BF16)
+        fill_normal_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((__nv_bfloat16*)out, n, key, mean, std_dev);
+    else if (out_dtype == ZLM_F32)
+        fill_normal_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>((float*)out, n, key, mean, std_dev);
     else
         return ZLM_ERR_UNSUPPORTED;
     return launch_status();

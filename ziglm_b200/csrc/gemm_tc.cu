@@ -130,7 +130,7 @@ __device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* t
 
     const int f = row0 + f_local;
     float bias_v = 0.f;
-    if (!GLU && a.bias != nullptr && f < a.N && add_bias)
+    if (a.bias != nullptr && f < a.N && add_bias)
         bias_v = a.bias_dtype == ZLM_F32 ? reinterpret_cast<const float*>(a.bias)[f]
                                         : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
     const int out_f = GLU ? f >> 1 : f;
@@ -386,7 +386,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             first_cluster_barrier_done = true;
             const int f = row0 + f_local;
             float bias_v = 0.f;
-            if (!GLU && a.bias != nullptr && f < a.N)
+            if (a.bias != nullptr && f < a.N)
                 bias_v = a.bias_dtype == ZLM_F32 ? reinterpret_cast<const float*>(a.bias)[f]
                                                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
             const int out_f = GLU ? f >> 1 : f;
@@ -876,8 +876,8 @@ static int pick_pair_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx
 using namespace zlm;
 
 // X: bf16 [T, K] (row stride ldx), W: bf16 [N, K] (row stride ldw), Y: float or bf16 [T, N] (row stride ldy).
-// glu: 0 = plain product; 1 / 2 = the rows of W alternate gate and up rows and Y is bf16 [T, N/2] holding
-//      silu(gate) * up (1) or tanh-gelu(gate) * up (2).
+// glu: 0 = plain product; 1 / 2 = the rows of W (and the entries of bias) alternate gate and up rows and Y is
+//      bf16 [T, N/2] holding silu(gate) * up (1) or tanh-gelu(gate) * up (2), the bias added before the activation.
 // splits: 0 = choose, else the number of CTAs a tile's K range is split over (1..8); 1 also keeps steps of more
 //      than 128 tokens on the one-CTA kernel (0 gives them to the kernel that pairs two CTAs per tile).
 // Refuses (ZLM_ERR_UNSUPPORTED) strides or addresses TMA cannot read; the caller falls back.
@@ -903,7 +903,7 @@ ZLM_EXPORT int zlm_gemm_tc_norm(const void* X, const void* W, const void* bias, 
     if (K <= 0 || ldx < K || ldw < K || ldy < n_out || splits < 0 || splits > 8 || glu < 0 || glu > 2)
         return ZLM_ERR_BAD_ARG;
     if (accumulate && y_dtype != ZLM_F32) return ZLM_ERR_BAD_ARG;
-    if (glu && ((N & 1) || y_dtype != ZLM_BF16 || bias != nullptr)) return ZLM_ERR_BAD_ARG;
+    if (glu && ((N & 1) || y_dtype != ZLM_BF16)) return ZLM_ERR_BAD_ARG;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return ZLM_ERR_UNSUPPORTED;
     // more than 64 tokens and at least two tiles of weight rows: two CTAs per tile of 256 rows x 256 tokens (with 65
     // to 128 tokens half of the tile is empty, which costs less than leaving the K split and the second SM out)
@@ -1003,4 +1003,10 @@ ZLM_EXPORT int zlm_gemm_tc_status(int* out) {
     if (e != cudaSuccess) return (int)e;
     if (*out != 0) cudaMemset(w, 0, sizeof(int));
     return 0;
+}
+
+// Runs the give-up path of the bounded waits once, harmlessly (see wait_selftest_kernel): afterwards
+// zlm_gemm_tc_status returns 90.  seen: two ints on the device.
+ZLM_EXPORT int zlm_gemm_tc_wait_selftest(int polls, int* seen, cudaStream_t stream) {
+    return run_wait_selftest(error_word(), polls, seen, stream);
 }

@@ -19,6 +19,7 @@ constexpr int ERR_WAIT_FULL = 1;      // consumer waited for a TMA tile that nev
 constexpr int ERR_WAIT_EMPTY = 2;     // producer waited for a stage that never drained
 constexpr int ERR_WAIT_ACCUM = 3;     // epilogue waited for accumulators that never completed
 constexpr int ERR_WAIT_DRAIN = 4;     // tail waited for copies in flight
+constexpr int ERR_SELFTEST = 90;      // the wait of wait_selftest_kernel, which is meant to run out
 
 constexpr uint32_t WAIT_POLLS = 1u << 22;   // each poll may itself block for a short, bounded time
 
@@ -58,8 +59,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Wait for the phase with the given parity to complete.  Returns false (and records
 // `code`) if it did not within the poll limit or if another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
-    for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                          uint32_t polls = WAIT_POLLS) {
+    for (uint32_t i = 0; i < polls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
@@ -307,6 +309,33 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
     return v;
+}
+
+// The give-up path of mbar_wait, run on purpose: one block initialises a barrier in its own shared memory
+// that nothing ever arrives on (no copy, no tensor memory, nothing in flight), waits on it with a small poll
+// limit, and reports.  seen[0] = what the wait returned (0: it gave up), seen[1] = the abort flag it left.
+// The error word receives ERR_SELFTEST, which the library's status call then returns and clears.
+static __global__ void wait_selftest_kernel(int* err, uint32_t polls, int* seen) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool passed = mbar_wait(smem_u32(&bar), 0, &abort_flag, err, ERR_SELFTEST, polls);
+        seen[0] = passed ? 1 : 0;
+        seen[1] = abort_flag;
+    }
+}
+
+static inline int run_wait_selftest(int* err_word, int polls, int* seen, cudaStream_t stream) {
+    if (!err_word || !seen || polls < 1 || polls > (1 << 20)) return -1;
+    wait_selftest_kernel<<<1, 32, 0, stream>>>(err_word, (uint32_t)polls, seen);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 }  // namespace tc

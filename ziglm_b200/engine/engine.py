@@ -315,6 +315,23 @@ class Engine:
         r.left -= 1
         return g.logits
 
+    # ------------------------------------------------------------- kernel health
+    def check_kernels(self, read=None) -> None:
+        """Raise :class:`~ziglm_b200.kernels.KernelError` if a bounded wait ran out inside a tensor-core kernel
+        since the last check.  Such a kernel returned early: the rows of its step are not to be trusted, and the
+        flat decode attention may have left its per-sequence counters non-zero.  Before raising, the counters of
+        every workspace are zeroed and the decode step kept for repetition is dropped, so that the engine can be
+        used again; the sequences that were live should be ended.  ``read``: a stand-in for
+        ``kernels.wait_errors`` (tests).  Synchronises the device."""
+        codes = (read or kernels.wait_errors)()
+        if not any(codes.values()):
+            return
+        self._repeat = None
+        for ws in [self.ws] + [g.ws for g in self._graphs.values()]:
+            ws.zero("attn_flat_counters")
+        raise kernels.KernelError("a bounded wait ran out inside a kernel, the step's results are not valid: "
+                                  + kernels.describe_wait_errors(codes))
+
     def graph_launched_kernels(self) -> int:
         """Kernels launched by graph replays since the counter was last read."""
         n, self._graph_kernels = self._graph_kernels, 0

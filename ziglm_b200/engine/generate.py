@@ -9,9 +9,11 @@ prompts, a request that ends gives its slot back at once while the others go on,
 and batch follows batch until every request is done.  Token ids go in and come
 out; tokenising is not part of this library.
 
-The loop only decides; everything that touches the device goes through the three
-calls of a *backend* (``alloc_slot``, ``free_slot``, ``step_and_sample``), so the
-decisions are tested without a GPU.
+The loop only decides; everything that touches the device goes through the calls
+of a *backend* (``alloc_slot``, ``free_slot``, ``step_and_sample`` and, if it has
+one, ``check``, which is called when a batch ends and raises if the device
+reported a fault), so the decisions are tested without a GPU.  If a step raises,
+the slots of the live sequences are given back before the error goes on.
 """
 from __future__ import annotations
 
@@ -113,47 +115,64 @@ def run_generation(backend, prompts: Sequence[Sequence[int]], options: Generatio
         batch = plan_batch(pending, prompt_lens, options.max_tokens, max_batch, max_tokens, max_seq_len, page)
         pending = pending[len(batch):]
         live = [_Live(r, backend.alloc_slot(), 0, [], list(prompts[r])) for r in batch]
-        first = True
-        while live:
-            t0 = time.perf_counter()
-            if first:
-                entries = [(s.slot, list(prompts[s.request])) for s in live]
-            else:
-                entries = [(s.slot, [s.next_token]) for s in live]
-            sampled = backend.step_and_sample(entries, [s.request for s in live], [s.history for s in live],
-                                              [len(s.out) for s in live], options.sampler)
-            dt = (time.perf_counter() - t0) * 1000.0
-            if first:
-                stats.prefill_time_ms += dt
-                stats.prompt_tokens += sum(len(e[1]) for e in entries)
-            else:
-                stats.generation_time_ms += dt
-            still: List[_Live] = []
-            for s, e, tok in zip(live, entries, sampled):
-                s.length += len(e[1])
-                tok = int(tok)
-                if tok in stop:
-                    finish(s, "stop")                                    # the stop token is not emitted
-                    continue
-                s.out.append(tok)
-                s.history.append(tok)
-                stats.completion_tokens += 1
-                keep_going = True
-                if callback is not None and callback(s.request, tok) is False:
-                    keep_going = False
-                if not keep_going:
-                    finish(s, "stop")
-                elif len(s.out) >= options.max_tokens:
-                    finish(s, "length")
-                elif s.length >= max_seq_len:
-                    finish(s, "context")                                 # cur_pos < max_seq_len, src/engine.zig:464
-                else:
-                    s.next_token = tok
-                    still.append(s)
-            live = still
-            first = False
+        try:
+            _run_batch(backend, live, True, prompts, options, stop, stats, finish, max_seq_len, callback)
+        except BaseException:
+            for s in live:
+                if results[s.request] is None:
+                    try:
+                        backend.free_slot(s.slot)
+                    except Exception:
+                        pass
+            raise
     stats.total_time_ms = (time.perf_counter() - t_start) * 1000.0
     return [r for r in results if r is not None], stats
+
+
+def _run_batch(backend, live: List[_Live], first: bool, prompts, options: GenerationOptions, stop, stats: GenerationStats,
+               finish, max_seq_len: int, callback) -> None:
+    """One batch from its prompts to its last sequence's end.  ``live`` is emptied as sequences end."""
+    while live:
+        t0 = time.perf_counter()
+        if first:
+            entries = [(s.slot, list(prompts[s.request])) for s in live]
+        else:
+            entries = [(s.slot, [s.next_token]) for s in live]
+        sampled = backend.step_and_sample(entries, [s.request for s in live], [s.history for s in live],
+                                          [len(s.out) for s in live], options.sampler)
+        dt = (time.perf_counter() - t0) * 1000.0
+        if first:
+            stats.prefill_time_ms += dt
+            stats.prompt_tokens += sum(len(e[1]) for e in entries)
+        else:
+            stats.generation_time_ms += dt
+        still: List[_Live] = []
+        for s, e, tok in zip(live, entries, sampled):
+            s.length += len(e[1])
+            tok = int(tok)
+            if tok in stop:
+                finish(s, "stop")                                    # the stop token is not emitted
+                continue
+            s.out.append(tok)
+            s.history.append(tok)
+            stats.completion_tokens += 1
+            keep_going = True
+            if callback is not None and callback(s.request, tok) is False:
+                keep_going = False
+            if not keep_going:
+                finish(s, "stop")
+            elif len(s.out) >= options.max_tokens:
+                finish(s, "length")
+            elif s.length >= max_seq_len:
+                finish(s, "context")                                 # cur_pos < max_seq_len, src/engine.zig:464
+            else:
+                s.next_token = tok
+                still.append(s)
+        live[:] = still
+        first = False
+    check = getattr(backend, "check", None)
+    if check is not None:
+        check()
 
 
 def generate(engine, prompts, options: Optional[GenerationOptions] = None, callback=None):

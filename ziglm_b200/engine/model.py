@@ -1,4 +1,5 @@
-"""The model: an embedding, blocks run in the order of the schedule, a final norm, a head.
+"""The model: an embedding, blocks run in the order of the schedule, a final norm, a head; an architecture
+may hang a part of its own behind the embedding and behind the head (``ModelSpec.embed_hook``, ``logits_hook``).
 
 Built from a :class:`~ziglm_b200.config.spec.ModelSpec` alone.  The forward pass
 is the reference's per-token loop (embedding src/model.zig:495-503, layers
@@ -15,7 +16,7 @@ import torch
 
 from .. import kernels
 from ..config.spec import ModelSpec
-from ..parts import Linear, ParamDecl, block_class, norm_class
+from ..parts import Linear, ParamDecl, block_class, hook_class, norm_class
 from ..parts.base import KVNeed, StateNeed
 from .batch import StepContext
 
@@ -30,6 +31,10 @@ def declare_parameters(spec: ModelSpec) -> Dict[str, ParamDecl]:
         out[_final_norm_name(spec, local)] = decl
     if spec.head_name is not None:
         out[spec.head_name] = ParamDecl((spec.vocab_size, spec.width))
+    for hook in (spec.embed_hook, spec.logits_hook):
+        if hook is not None:
+            for local, decl in hook_class(hook.kind).declare(hook).items():
+                out[hook.names.get(local, local)] = decl
     return out
 
 
@@ -47,6 +52,8 @@ class Model:
         self.device = device
         self.blocks = [block_class(layer.block)(layer, dtype, device) for layer in spec.layers]
         self.final_norm = norm_class(spec.final_norm.kind)(spec.final_norm, dtype, device)
+        self.embed_hook = hook_class(spec.embed_hook.kind)(spec.embed_hook, dtype, device) if spec.embed_hook else None
+        self.logits_hook = hook_class(spec.logits_hook.kind)(spec.logits_hook, dtype, device) if spec.logits_hook else None
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
 
@@ -64,6 +71,10 @@ class Model:
                               for name in norm_class(spec.final_norm.kind).declare(spec.final_norm)})
         head_weight = self.embedding if spec.head_name is None else tensors[spec.head_name]
         self.head = Linear(head_weight)
+        for hook_spec, hook in ((spec.embed_hook, self.embed_hook), (spec.logits_hook, self.logits_hook)):
+            if hook is not None:
+                hook.bind({local: tensors[hook_spec.names.get(local, local)]
+                           for local in hook_class(hook_spec.kind).declare(hook_spec)})
 
     def kernel_libraries(self) -> Tuple[str, ...]:
         libs = ("elementwise",) + self.final_norm.kernel_libraries()
@@ -71,6 +82,9 @@ class Model:
             libs += b.kernel_libraries()
         if self.head is not None:
             libs += self.head.libraries(self.dtype)
+        for hook in (self.embed_hook, self.logits_hook):
+            if hook is not None:
+                libs += hook.kernel_libraries()
         return tuple(dict.fromkeys(libs))
 
     # ----------------------------------------------------- what the cache must hold
@@ -101,6 +115,8 @@ class Model:
         spec = self.spec
         x = step.ws.buf("residual", (step.n_tokens, spec.width), torch.float32)
         kernels.embed(self.embedding, step.tokens, x, spec.embedding_scale)
+        if self.embed_hook is not None:
+            self.embed_hook.forward(step, x)
         carried = None           # the next block's first norm, half done by the block before (steps of few tokens)
         for place, li in enumerate(spec.schedule):
             block = self.blocks[li]
@@ -116,4 +132,6 @@ class Model:
         h = self.final_norm.forward(step, x, rows=step.want_rows, n_rows=step.n_want, name="final_norm_out")
         logits = step.ws.buf("logits", (step.n_want, spec.vocab_size), torch.float32)
         self.head(h, logits)
+        if self.logits_hook is not None:
+            self.logits_hook.forward(step, logits)
         return logits

@@ -31,5 +31,11 @@ class Workspace:
             self._flat[key] = flat
         return flat[:n].view(*shape)
 
+    def zero(self, name: str) -> None:
+        """Set every buffer of this name to zero (whatever its element type)."""
+        for (n, _), flat in self._flat.items():
+            if n == name:
+                flat.zero_()
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._flat.values())

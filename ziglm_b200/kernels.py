@@ -55,6 +55,7 @@ _PROTOTYPES = {
         "zlm_gated_act": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "zlm_add": [c_void_p, c_void_p, c_long, c_void_p],
         "zlm_convert": [c_void_p, c_int, c_void_p, c_int, c_long, c_void_p],
+        "zlm_fill_normal": [c_void_p, c_int, c_long, ctypes.c_ulonglong, c_float, c_float, c_void_p],
     },
     "gemm_generic": {
         "zlm_gemm_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -78,12 +79,14 @@ _PROTOTYPES = {
         "zlm_attention_prefill": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_void_p],
         "zlm_attention_tc_status": [c_void_p],
+        "zlm_attention_tc_wait_selftest": [c_int, c_void_p, c_void_p],
     },
     "attention_fmha": {
         "zlm_attention_prefill_fmha": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                        c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int,
                                        c_void_p],
         "zlm_attention_fmha_status": [c_void_p],
+        "zlm_attention_fmha_wait_selftest": [c_int, c_void_p, c_void_p],
     },
     "gemm_tc": {
         "zlm_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -92,6 +95,7 @@ _PROTOTYPES = {
                              c_long, c_long, c_long, c_int, c_void_p, c_int, c_float, c_void_p, c_long, c_void_p,
                              c_void_p, c_void_p, c_int, c_float, c_void_p],
         "zlm_gemm_tc_status": [c_void_p],
+        "zlm_gemm_tc_wait_selftest": [c_int, c_void_p, c_void_p],
     },
     "sampling": {
         "zlm_sample_parts_scratch": [c_int],
@@ -209,6 +213,15 @@ def convert(src: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("convert: sizes differ")
     _check(_fn("elementwise", "zlm_convert")(src.data_ptr(), code(src.dtype), out.data_ptr(), code(out.dtype),
                                              src.numel(), _stream()), "convert")
+
+
+def fill_normal(out: torch.Tensor, key: int, mean: float, std: float) -> None:
+    """out.flat[i] = mean + std * z(key, i) with z the counter-based standard normal value of
+    ``ziglm_b200.weights.random_init.normal_values`` (the same bits on the device as there)."""
+    _cuda(out, "out")
+    _check(_fn("elementwise", "zlm_fill_normal")(out.data_ptr(), code(out.dtype), out.numel(),
+                                                 int(key) & 0xFFFFFFFFFFFFFFFF, float(mean), float(std), _stream()),
+           "fill_normal")
 
 
 # ------------------------------------------------------------------------ gemm
@@ -539,8 +552,9 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
                       io.block_table, io.k_pages, io.v_pages, io.page_size)
 
 
-def fast_attention_libraries(dtype: torch.dtype, head_dim: int):
-    return ("attention_tc", "attention_fmha") if dtype == torch.bfloat16 and head_dim in (64, 128) else ()
+def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1, n_kv: int = 1):
+    """The sources of the tensor-core attention kernels if they take this shape, else nothing (the plain kernel runs)."""
+    return ("attention_tc", "attention_fmha") if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
 
 
 def fast_gemm_libraries():
@@ -554,8 +568,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
             accumulate: bool = False, splits: int = 0, glu: Optional[str] = None, norm_out=None, row_scale=None):
     """out[T,N] (+)= x[T,K] @ w[N,K]^T (+ bias) on the tcgen05 tensor cores, bf16 operands.
 
-    With ``glu`` ("silu" or "gelu_tanh") the rows of w alternate gate and up rows and out is bf16 [T, N/2]
-    holding act(gate) * up.
+    With ``glu`` ("silu" or "gelu_tanh") the rows of w (and the entries of bias) alternate gate and up rows and
+    out is bf16 [T, N/2] holding act(gate + bias) * (up + bias).
 
     An RMSNorm between two products of a step of few tokens can ride on them.  ``norm_out`` = (gain, offset, hb,
     ssq) on the product before it (``accumulate`` into the float32 residual): it also leaves bf16(x * (gain +
@@ -577,8 +591,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
     T, K = x.shape
     N = w.shape[0]
     n_out = N // 2 if glu else N
-    if glu and (glu not in GLU_KINDS or N % 2 or out.dtype != torch.bfloat16 or bias is not None):
-        raise KernelError("gemm_tc: the gated mode needs silu or gelu_tanh, an even row count, a bf16 output, no bias")
+    if glu and (glu not in GLU_KINDS or N % 2 or out.dtype != torch.bfloat16):
+        raise KernelError("gemm_tc: the gated mode needs silu or gelu_tanh, an even row count and a bf16 output")
     if w.shape[1] != K or out.shape != (T, n_out):
         raise KernelError(f"gemm: shapes do not match: x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     if accumulate and out.dtype != torch.float32:
@@ -624,6 +638,45 @@ def gemm_tc_status() -> int:
     if rc != 0:
         raise KernelError(f"gemm_tc_status: CUDA error {rc}")
     return out.value
+
+
+WAIT_ERROR_NAMES = {
+    1: "a tile never landed", 2: "a stage never drained", 3: "an accumulator never completed",
+    4: "copies were still in flight when a block gave up", 11: "a cache page never landed",
+    12: "a stage never drained", 21: "the queries never landed", 22: "a cache page never landed",
+    23: "the scores never completed", 24: "the probabilities were never consumed", 25: "the output never completed",
+    26: "a stage never drained", 27: "a tile address was off its boundary", 90: "a wait ran out on purpose (self-test)",
+}
+
+
+def wait_errors() -> dict:
+    """The error words of the bounded waits of every tensor-core library this process has loaded: library name
+    -> code (0: none).  Reading a word clears it.  Synchronises the device."""
+    out = {}
+    for lib, read in (("gemm_tc", gemm_tc_status), ("attention_tc", attention_tc_status),
+                      ("attention_fmha", attention_fmha_status)):
+        if _build.is_loaded(lib):
+            out[lib] = read()
+    return out
+
+
+def wait_selftest(library: str, polls: int = 4096) -> Tuple[int, int]:
+    """Run the give-up path of the bounded waits of ``library`` ("gemm_tc", "attention_tc" or "attention_fmha")
+    once, on purpose and harmlessly: one block waits, with a limit of ``polls`` polls, on a barrier in its own
+    shared memory that nothing arrives on (no copy, no tensor memory, nothing in flight), records code 90 in
+    the library's error word and returns.  Result: (what the wait returned: 0 = gave up, the abort flag it
+    left).  The library's status call then reports 90 once."""
+    if library not in ("gemm_tc", "attention_tc", "attention_fmha"):
+        raise KernelError(f"no bounded waits in {library!r}")
+    seen = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    _check(_fn(library, f"zlm_{library}_wait_selftest")(int(polls), seen.data_ptr(), _stream()), "wait_selftest")
+    torch.cuda.current_stream().synchronize()
+    passed, flag = seen.tolist()
+    return int(passed), int(flag)
+
+
+def describe_wait_errors(codes: dict) -> str:
+    return "; ".join(f"{lib}: code {c} ({WAIT_ERROR_NAMES.get(c, 'unknown')})" for lib, c in codes.items() if c)
 
 
 def fast_gemm(linear, x: torch.Tensor, out: torch.Tensor, accumulate: bool, norm_out=None, row_scale=None):

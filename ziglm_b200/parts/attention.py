@@ -18,6 +18,7 @@ keys and values (the reference's shared-KV layers, src/model.zig:599-618).
 from __future__ import annotations
 
 import math
+import warnings
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -26,6 +27,9 @@ from .. import kernels
 from ..config.spec import MixerSpec
 from .base import KVNeed, LayerIO, ParamDecl, Part, StateNeed, position_class, register_mixer
 from .linear import Linear
+
+
+_warned = set()      # (head size, group) pairs whose slow path has been announced
 
 
 class Attention(Part):
@@ -40,8 +44,21 @@ class Attention(Part):
         self.scale = float(spec.scale) if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
         self.window = spec.window
         self.position = position_class(spec.position.kind)(spec.position, dtype, device)
+        score_scale = getattr(self.position, "score_scale", None)
+        if score_scale is not None:
+            self.scale *= float(score_scale(spec.head_dim))
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
+        if dtype == torch.bfloat16 and not kernels.fast_attention_libraries(dtype, spec.head_dim, spec.n_heads,
+                                                                            spec.n_kv_heads):
+            key = (spec.head_dim, spec.n_heads // spec.n_kv_heads)
+            if key not in _warned:
+                _warned.add(key)
+                warnings.warn(
+                    f"attention with head size {spec.head_dim} and {key[1]} query heads per key/value head runs on the "
+                    "plain CUDA-core kernel, which is right but many times slower than the tensor-core kernels "
+                    "(those take head sizes 64 and 128 with at most 16 query heads per key/value head)",
+                    RuntimeWarning, stacklevel=2)
 
     @classmethod
     def declare(cls, spec: MixerSpec) -> Dict[str, ParamDecl]:
@@ -73,7 +90,7 @@ class Attention(Part):
         self.o = Linear(tensors["o.weight"], tensors.get("o.bias") if self.spec.out_bias else None)
 
     def kernel_libraries(self) -> Tuple[str, ...]:
-        libs = ("attention",) + kernels.fast_attention_libraries(self.dtype, self.head_dim)
+        libs = ("attention",) + kernels.fast_attention_libraries(self.dtype, self.head_dim, self.n_heads, self.n_kv)
         for lin in (self.qkv, self.o):
             if lin is not None:
                 libs += lin.libraries(self.dtype)

@@ -17,6 +17,9 @@ Mixer           ``cache_needs() -> KVNeed | None``, ``state_needs() -> StateNeed
                 in the schedule that is running (:class:`LayerIO`).
 FeedForward     ``forward(step, h, residual)``: adds its output to ``residual``.
 Block           ``forward(step, io, x)``: runs its parts on the residual stream x.
+Hook            ``forward(step, x)``: changes x in place; x is the float32 residual
+                [T, d] after the embedding (``ModelSpec.embed_hook``) or the float32
+                logits [n_want, vocab] (``ModelSpec.logits_hook``).
 
 A norm that rides on its neighbours
 -----------------------------------
@@ -106,7 +109,8 @@ class Part:
         return ()
 
 
-_REGISTRIES: Dict[str, Dict[str, Any]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}}
+_REGISTRIES: Dict[str, Dict[str, Any]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {},
+                                          "hook": {}}
 
 
 def _register(family: str, kind: str, cls: Any) -> None:
@@ -129,6 +133,7 @@ def register_position(kind: str, cls: Any) -> None: _register("position", kind, 
 def register_mixer(kind: str, cls: Any) -> None: _register("mixer", kind, cls)
 def register_feed_forward(kind: str, cls: Any) -> None: _register("feed_forward", kind, cls)
 def register_block(kind: str, cls: Any) -> None: _register("block", kind, cls)
+def register_hook(kind: str, cls: Any) -> None: _register("hook", kind, cls)
 
 
 def unregister(family: str, kind: str) -> None:
@@ -140,3 +145,4 @@ def position_class(kind: str) -> Any: return _lookup("position", kind)
 def mixer_class(kind: str) -> Any: return _lookup("mixer", kind)
 def feed_forward_class(kind: str) -> Any: return _lookup("feed_forward", kind)
 def block_class(kind: str) -> Any: return _lookup("block", kind)
+def hook_class(kind: str) -> Any: return _lookup("hook", kind)

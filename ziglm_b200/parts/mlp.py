@@ -2,7 +2,8 @@
 
 The reference computes g = W_g x, u = W_u x, act_j = silu(g_j) u_j with
 silu(z) = z/(1+exp(-z)), f = W_d act, no biases (src/model.zig:725-745,
-src/math.zig:1108-1117); its GPU path applies the tanh GELU to every
+src/math.zig:1108-1117; biases b_g, b_u, b_d are added to the three products when
+the spec asks for them); its GPU path applies the tanh GELU to every
 architecture (src/cuda_model.zig:695,1379), which is not reproduced.  Gate and
 up are one matrix product over the concatenated weight [gate; up]; the
 activation is a parameter of the part.  On the bfloat16 path the rows of that
@@ -26,8 +27,6 @@ class GatedMLP(Part):
         super().__init__(spec, dtype, device)
         if spec.activation not in ("silu", "gelu_tanh"):
             raise ValueError(f"gated_mlp: activation {spec.activation!r} is not known (silu, gelu_tanh)")
-        if spec.bias:
-            raise ValueError("gated_mlp: biases are not supported")
         self.intermediate = spec.intermediate
         self.interleaved = False
         self.gate_up: Optional[Linear] = None
@@ -35,19 +34,30 @@ class GatedMLP(Part):
 
     @classmethod
     def declare(cls, spec: FeedForwardSpec) -> Dict[str, ParamDecl]:
-        return {"gate.weight": ParamDecl((spec.intermediate, spec.width)),
-                "up.weight": ParamDecl((spec.intermediate, spec.width)),
-                "down.weight": ParamDecl((spec.width, spec.intermediate))}
+        p = {"gate.weight": ParamDecl((spec.intermediate, spec.width)),
+             "up.weight": ParamDecl((spec.intermediate, spec.width)),
+             "down.weight": ParamDecl((spec.width, spec.intermediate))}
+        if spec.bias:
+            p["gate.bias"] = ParamDecl((spec.intermediate,))
+            p["up.bias"] = ParamDecl((spec.intermediate,))
+            p["down.bias"] = ParamDecl((spec.width,))
+        return p
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors["gate.weight"], tensors["up.weight"]
         wide = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
         self.interleaved = self.dtype == torch.bfloat16 and wide == torch.bfloat16
+        bias = None
+        if self.spec.bias:
+            bg, bu = tensors["gate.bias"], tensors["up.bias"]
+            bwide = torch.float32 if torch.float32 in (bg.dtype, bu.dtype) else bg.dtype
+            parts = [bg.to(bwide), bu.to(bwide)]
+            bias = torch.stack(parts, dim=1).reshape(-1) if self.interleaved else torch.cat(parts, dim=0)
         if self.interleaved:
-            self.gate_up = Linear(torch.stack([g, u], dim=1).reshape(2 * self.intermediate, -1))
+            self.gate_up = Linear(torch.stack([g, u], dim=1).reshape(2 * self.intermediate, -1), bias)
         else:
-            self.gate_up = Linear(torch.cat([g.to(wide), u.to(wide)], dim=0))
-        self.down = Linear(tensors["down.weight"])
+            self.gate_up = Linear(torch.cat([g.to(wide), u.to(wide)], dim=0), bias)
+        self.down = Linear(tensors["down.weight"], tensors["down.bias"] if self.spec.bias else None)
 
     def kernel_libraries(self) -> Tuple[str, ...]:
         libs = ("elementwise",)
@@ -66,7 +76,8 @@ class GatedMLP(Part):
         act = step.ws.buf("ffn_act", (T, self.intermediate), self.dtype)
         normed = isinstance(h, NormedInput)
         rows = h.hb if normed else h
-        fused = self.interleaved and kernels.gemm_tc(rows, self.gate_up.weight, act, glu=self.spec.activation,
+        fused = self.interleaved and kernels.gemm_tc(rows, self.gate_up.weight, act, bias=self.gate_up.bias,
+                                                     glu=self.spec.activation,
                                                      row_scale=(h.ssq, h.eps) if normed else None)
         if not fused:
             gu = step.ws.buf("gate_up", (T, 2 * self.intermediate), self.dtype)

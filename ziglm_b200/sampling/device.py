@@ -11,10 +11,16 @@ from .rng import request_seed
 
 
 class DeviceSampler:
-    """``alloc_slot``/``free_slot``/``step_and_sample`` for :func:`ziglm_b200.engine.generate.run_generation`."""
+    """``alloc_slot``/``free_slot``/``step_and_sample``/``check`` for
+    :func:`ziglm_b200.engine.generate.run_generation`.
+
+    The error words of the kernels' bounded waits are read every ``CHECK_EVERY`` steps and when the loop asks
+    (at the end of every batch); a non-zero word ends the generation with a ``KernelError``."""
+    CHECK_EVERY = 16
 
     def __init__(self, engine):
         self.engine = engine
+        self._steps = 0
         self.device = engine.device
         self._out = torch.empty(1024, dtype=torch.int32, device=self.device)
         self._out_host = torch.empty(1024, dtype=torch.int32).pin_memory()
@@ -54,4 +60,11 @@ class DeviceSampler:
                         histories: Sequence[Sequence[int]], counters: Sequence[int],
                         params: SamplerParams) -> List[int]:
         logits = self.engine.step(entries)
-        return self.sample_logits(logits, requests, histories, counters, params)
+        sampled = self.sample_logits(logits, requests, histories, counters, params)
+        self._steps += 1
+        if self._steps % self.CHECK_EVERY == 0:
+            self.check()
+        return sampled
+
+    def check(self) -> None:
+        self.engine.check_kernels()
