@@ -184,6 +184,78 @@ def test_first_tokens_of_a_sequence(zoo, name, dn):
         helpers.assert_close(got, want, DTYPES[dn], f"{name} {dn} first tokens whole {toks}")
 
 
+@pytest.mark.parametrize("name,dn", [("D", "bfloat16"), ("E", "bfloat16"), ("F", "bfloat16"), ("D", "float32")])
+def test_a_prompt_in_pieces_on_a_slot_that_already_holds_tokens(zoo, name, dn):
+    """A prompt of 150 tokens cut into 70 + 50 + 30: the second and third piece are prompt steps of many tokens
+    on a slot that is not empty (in bfloat16 with head size 64 or 128 that is the tcgen05 prompt kernel reading
+    cached pages before the new tokens).  Every place is wanted and compared with the plain model."""
+    folder, eng = zoo.get(name, dn)
+    V = helpers.CONFIGS[name]["vocab_size"]
+    toks = helpers.random_tokens(150, V, 4242)
+    want = helpers.plain_logits(folder, toks, act=None if dn == "float32" else torch.bfloat16)
+    slot = eng.alloc_slot()
+    rows, at = [], 0
+    for n in (70, 50, 30):
+        rows.append(eng.step([(slot, toks[at:at + n])], [list(range(n))]).clone())
+        at += n
+    eng.free_slot(slot)
+    helpers.assert_close(torch.cat(rows), want, DTYPES[dn], f"{name} {dn} prompt in pieces 70 + 50 + 30")
+    # and two sequences at different depths in one step: 20 new tokens after 70, 45 new tokens after 16
+    other = helpers.random_tokens(61, V, 4243)
+    want_other = helpers.plain_logits(folder, other, act=None if dn == "float32" else torch.bfloat16)
+    a, b = eng.alloc_slot(), eng.alloc_slot()
+    eng.step([(a, toks[:70]), (b, other[:16])], [[], []])
+    got = eng.step([(a, toks[70:90]), (b, other[16:61])], [list(range(20)), list(range(45))]).clone()
+    eng.free_slot(a); eng.free_slot(b)
+    helpers.assert_close(got[:20], want[70:90], DTYPES[dn], f"{name} {dn} 20 tokens after 70")
+    helpers.assert_close(got[20:], want_other[16:61], DTYPES[dn], f"{name} {dn} 45 tokens after 16")
+
+
+@pytest.mark.parametrize("name,dn", [("D", "float32"), ("D", "bfloat16"), ("E", "bfloat16")])
+def test_a_batch_that_shrinks_through_many_sizes_generates_what_each_request_generates_alone(tmp_path, name, dn):
+    """Twelve requests on eight slots, each ended after its own number of tokens, so the batch steps down through
+    most sizes from 8 to 1 (twice).  In float32, where logits do not depend on the batch, greedy output equals
+    one request at a time token for token.  In bfloat16 a batch and a single request take different kernels for
+    their prompts, so two nearly equal logits may be ordered differently; there every token that was chosen must
+    be the plain model's best for its place up to the comparison's tolerance."""
+    from ziglm_b200 import Engine, EngineOptions, GenerationOptions, SamplerParams
+    # a larger spread of the weights separates the logits
+    dtype = DTYPES[dn]
+    folder = helpers.make_folder(tmp_path, helpers.CONFIGS[name], 29, dtype, helpers.NORM_JITTER[name], std=0.08)
+    eng = Engine.load(folder, EngineOptions(dtype=dn, max_batch=8, max_tokens=2048))
+    V = helpers.CONFIGS[name]["vocab_size"]
+    prompts = [helpers.random_tokens(5 + 7 * i, V, 300 + i) for i in range(12)]
+    limits = [3, 9, 14, 6, 21, 11, 17, 25, 4, 8, 13, 2]
+    counts = {}
+
+    def stop_at_limit(request, token):
+        counts[request] = counts.get(request, 0) + 1
+        return counts[request] < limits[request]
+
+    opts = GenerationOptions(max_tokens=64, ignore_eos=True, sampler=SamplerParams(greedy=True))
+    together, _ = eng.generate(prompts, opts, callback=stop_at_limit)
+    assert [len(r.tokens) for r in together] == limits
+    assert len(eng._graphs) >= 5                            # the batch went through at least five sizes
+    eng.cache.slots.check()
+    assert eng.cache.slots.slots.n_held == 0
+    if dn == "float32":
+        for i, p in enumerate(prompts):
+            counts.clear()
+            alone, _ = eng.generate([p], opts, callback=lambda r, t, i=i: stop_at_limit(i, t))
+            assert alone[0].tokens == together[i].tokens, f"request {i}"
+    else:
+        tol = helpers.TOL[dtype]
+        for i, p in enumerate(prompts):
+            logits = helpers.plain_logits(folder, list(p) + together[i].tokens, act=dtype)
+            for k, tok in enumerate(together[i].tokens):
+                row = logits[len(p) - 1 + k]
+                slack = 2 * (tol["atol"] + tol["rtol"] * row.max().abs().item())
+                assert row[tok].item() >= row.max().item() - slack, f"request {i}, token {k}"
+    # what the graphs of all batch sizes hold beside the model
+    held = sum(g.ws.bytes() for g in eng._graphs.values())
+    assert held < 64 * 1024 * 1024, f"decode graphs hold {held} bytes of scratch"
+
+
 def test_wanted_places_and_nothing_wanted(zoo):
     folder, eng = zoo.get("A", "float32")
     toks = helpers.random_tokens(20, 256, 3)
