@@ -2,7 +2,11 @@
 """Decode and prefill throughput of the Llama-3.1-8B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
-    python bench.py --case prefill|decode [--layers L] [--batch B] [--context C]    one phase alone, for profilers
+    python bench.py --case prefill|decode [--shape 8b|1b|13b] [--dtype bfloat16|float32] [--layers L] [--batch B]
+                    [--context C] [--prompt-tokens T]                 one phase alone (for profilers and sweeps)
+    python bench.py --case workload-1b      64 prompts of 16..1,024 tokens in one step, then 128 steps (1B shape)
+    python bench.py --case workload-13b     8 prompts of 2,048 tokens, then 256 steps (13B shape)
+    python bench.py --case float32 [--layers L]    the 8B shape in true 32-bit: a 2,048-token prompt, decode at batch 1 and 8
     python bench.py --case reference-kernels [--context C]     the reference's CUDA kernels alone, if they were built
 
 A "step" is one decode step of a batch of 8 sequences at a context of 4096
@@ -41,6 +45,25 @@ LLAMA_8B = {
     "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
     "attention_bias": False,
 }
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "attention_bias": False,
+}
+LLAMA_13B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 5120, "intermediate_size": 13824, "num_hidden_layers": 40,
+    "num_attention_heads": 40, "num_key_value_heads": 40, "head_dim": 128, "vocab_size": 32000,
+    "rope_theta": 10000.0, "rope_scaling": None,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "attention_bias": False,
+}
+SHAPES = {"8b": LLAMA_8B, "1b": LLAMA_1B, "13b": LLAMA_13B}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -113,29 +136,40 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
-def decode_bytes(cfg, n_layers, batch, context, bytes_per_el=2):
-    """Bytes a decode step has to read: every weight it uses once and the cache of the live requests."""
+def decode_bytes(cfg, n_layers, batch, context, bytes_per_el=2, cached_tokens=None):
+    """Bytes a decode step has to read: every weight it uses once and the cache of the live requests
+    (``cached_tokens``: the sum of their lengths; default batch * context).  A tied head is the embedding
+    table, read once as the head; an untied model reads its head and `batch` rows of the embedding."""
     d, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     q = cfg["num_attention_heads"] * cfg["head_dim"]
     kv = cfg["num_key_value_heads"] * cfg["head_dim"]
     per_layer = d * q + 2 * d * kv + q * d + 3 * d * i + 2 * d
-    weights = n_layers * per_layer + v * d + d                 # the head; the embedding is read for `batch` rows only
-    cache = n_layers * 2 * kv * context * batch
+    weights = n_layers * per_layer + v * d + d
+    if cached_tokens is None:
+        cached_tokens = context * batch
+    cache = n_layers * 2 * kv * cached_tokens
     return (weights + cache) * bytes_per_el + batch * d * bytes_per_el
 
 
-def prefill_flops(cfg, n_layers, tokens):
+def prefill_flops(cfg, n_layers, tokens, wanted=1):
+    """FLOPs of one prompt of ``tokens`` tokens whose last ``wanted`` places go through the head."""
     d, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     q = cfg["num_attention_heads"] * cfg["head_dim"]
     kv = cfg["num_key_value_heads"] * cfg["head_dim"]
     linear = 2 * tokens * (d * q + 2 * d * kv + q * d + 3 * d * i)
     attn = 2 * 2 * q * tokens * (tokens + 1) / 2               # QK^T and PV over the causal half
-    return n_layers * (linear + attn) + 2 * d * v              # the head runs on the last token only
+    return n_layers * (linear + attn) + wanted * 2 * d * v
+
+
+def wait_errors(kernels):
+    """The error words of the kernels' bounded waits, as a list in a fixed order (0: none)."""
+    codes = kernels.wait_errors()
+    return [codes.get(k, 0) for k in ("gemm_tc", "attention_tc", "attention_fmha")]
 
 
 def run_ours(args):
     import torch
-    from ziglm_b200 import Engine, EngineOptions, GenerationOptions, SamplerParams, config_from_dict, kernels
+    from ziglm_b200 import Engine, EngineOptions, SamplerParams, config_from_dict, kernels
     from ziglm_b200.sampling.device import DeviceSampler
 
     torch.cuda.set_device(0)
@@ -147,6 +181,7 @@ def run_ours(args):
     steps, warmup = args.steps, max(3, args.warmup)
     slack = 64
     max_seq = CONTEXT + slack
+    kernels.require(("sampling",))
 
     def make_engine(batch):
         opts = EngineOptions(dtype="bfloat16", max_batch=batch, max_seq_len=max_seq,
@@ -169,22 +204,47 @@ def run_ours(args):
                 done += n
         return slots
 
-    def time_decode(engine, slots, n_warm, n_steps, flush=None):
-        """Device time of n_steps decode steps (ms per step) and the kernels launched in them."""
+    def time_decode(engine, slots, n_warm, n_steps):
+        """Device time of n_steps decode steps, each with its greedy choice on the device (ms per step), and
+        the kernels launched in them."""
         ids = [random_ids(len(slots)) for _ in range(n_warm + n_steps)]
+        picked = torch.empty(len(slots), dtype=torch.int32, device="cuda")
         for k in range(n_warm):
-            engine.step([(s, [t]) for s, t in zip(slots, ids[k])])
+            kernels.argmax(engine.step([(s, [t]) for s, t in zip(slots, ids[k])]), picked)
         torch.cuda.synchronize()
         kernels.reset_launches()
+        engine.graph_launched_kernels()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for k in range(n_warm, n_warm + n_steps):
-            engine.step([(s, [t]) for s, t in zip(slots, ids[k])])
+            kernels.argmax(engine.step([(s, [t]) for s, t in zip(slots, ids[k])]), picked)
         end.record()
         torch.cuda.synchronize()
         return start.elapsed_time(end) / n_steps, kernels.launches() + engine.graph_launched_kernels()
 
-    result = {}
+    def time_end_to_end(engine, slots, n_warm, n_steps):
+        """The same loop through the Python entry point: host token ids in (pinned memory, one copy a step),
+        the chosen ids read back every step.  Wall-clock ms per step and the bytes copied in a step."""
+        sampler = DeviceSampler(engine)
+        params = SamplerParams(greedy=True)
+        batch = len(slots)
+        tokens = random_ids(batch)
+        for k in range(n_warm):
+            tokens = sampler.step_and_sample([(s, [t]) for s, t in zip(slots, tokens)], list(range(batch)),
+                                             [[]] * batch, [k] * batch, params)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for k in range(n_steps):
+            tokens = sampler.step_and_sample([(s, [t]) for s, t in zip(slots, tokens)], list(range(batch)),
+                                             [[]] * batch, [k] * batch, params)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) * 1000.0 / n_steps, engine.last_step_h2d_bytes
+
+    def frac(batch, ms):
+        return decode_bytes(cfg, n_layers, batch, CONTEXT) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
+
+    # each phase starts so far below the context that its warm-up and timed steps end at it
+    start_ctx = max(1, CONTEXT - (warmup + steps) - 1)
     # ---------------------------------------------------------------- prefill, 2048 tokens of one sequence
     engine = make_engine(8)
     prompt = random_ids(PREFILL_TOKENS)
@@ -202,59 +262,48 @@ def run_ours(args):
         engine.free_slot(slot)
     pre_ms = sorted(times)[len(times) // 2]
     flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
-    result["prefill"] = {"value": round(PREFILL_TOKENS / pre_ms * 1000.0, 1), "tokens": PREFILL_TOKENS,
-                         "ms": round(pre_ms, 3),
-                         "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    prefill = {"value": round(PREFILL_TOKENS / pre_ms * 1000.0, 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---------------------------------------------------------------- decode, batch 8 at the context length
     batch = 8
-    start_ctx = CONTEXT - (warmup + steps) - 1
-    slots = fill(engine, batch, max(1, start_ctx))
+    slots = fill(engine, batch, start_ctx)
     with ClockSampler() as clocks:
         ms, launched = time_decode(engine, slots, warmup, steps)
     clock_summary = clocks.summary()
     tok_s = batch / ms * 1000.0
     bytes_step = decode_bytes(cfg, n_layers, batch, CONTEXT)
     achieved = bytes_step / (ms * 1e-3) / 1e9
-
-    # ---------------------------------------------------------------- the same through the Python entry point
-    sampler = DeviceSampler(engine)
-    params = SamplerParams(greedy=True)
-    pinned = torch.empty(batch, dtype=torch.int32).pin_memory()
     for s in slots:
         engine.free_slot(s)
-    slots = fill(engine, batch, max(1, start_ctx))
-    tokens = random_ids(batch)
-    e2e_steps = steps
-    for k in range(warmup):
-        tokens = sampler.step_and_sample([(s, [t]) for s, t in zip(slots, tokens)], list(range(batch)),
-                                         [[]] * batch, [k] * batch, params)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for k in range(e2e_steps):
-        tokens = sampler.step_and_sample([(s, [t]) for s, t in zip(slots, tokens)], list(range(batch)),
-                                         [[]] * batch, [k] * batch, params)
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1000.0 / e2e_steps
-    h2d = engine.last_step_h2d_bytes
+    slots = fill(engine, batch, start_ctx)
+    e2e_ms, h2d = time_end_to_end(engine, slots, warmup, steps)
     for s in slots:
         engine.free_slot(s)
-    del sampler
 
     # ---------------------------------------------------------------- decode at batch 1 and 64
     points = {}
-    s1 = fill(engine, 1, max(1, start_ctx))
+    s1 = fill(engine, 1, start_ctx)
     ms1, _ = time_decode(engine, s1, warmup, steps)
-    points["decode_b1"] = round(1 / ms1 * 1000.0, 1)
+    engine.free_slot(s1[0])
+    s1 = fill(engine, 1, start_ctx)
+    e2e1, _ = time_end_to_end(engine, s1, warmup, steps)
     engine.free_slot(s1[0])
     del engine
     torch.cuda.empty_cache()
     engine = make_engine(64)
-    s64 = fill(engine, 64, max(1, start_ctx))
+    s64 = fill(engine, 64, start_ctx)
     ms64, _ = time_decode(engine, s64, warmup, steps)
+    for s in s64:
+        engine.free_slot(s)
+    s64 = fill(engine, 64, start_ctx)
+    e2e64, _ = time_end_to_end(engine, s64, warmup, steps)
+    points["decode_b1"] = round(1 / ms1 * 1000.0, 1)
     points["decode_b64"] = round(64 / ms64 * 1000.0, 1)
-    points["decode_b1_hbm_frac"] = round(decode_bytes(cfg, n_layers, 1, CONTEXT) / (ms1 * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
-    points["decode_b64_hbm_frac"] = round(decode_bytes(cfg, n_layers, 64, CONTEXT) / (ms64 * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    points["decode_b1_hbm_frac"] = round(frac(1, ms1), 4)
+    points["decode_b64_hbm_frac"] = round(frac(64, ms64), 4)
+    points["e2e_b1"] = round(1 / e2e1 * 1000.0, 1)
+    points["e2e_b64"] = round(64 / e2e64 * 1000.0, 1)
 
     line = {
         "metric": "decode tok/s at batch 8 (Llama-3.1-8B shape, context 4096)",
@@ -274,66 +323,200 @@ def run_ours(args):
         "e2e": {"value": round(batch / e2e_ms * 1000.0, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": batch * 4},
         "gpu_launches": int(launched),
-        "prefill": result["prefill"],
+        "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
         "clocks": clock_summary,
+        "wait_errors": wait_errors(kernels),
     }
     print(json.dumps(line))
     return 0
 
 
-def run_case(args):
-    """A single phase on a (possibly shallower) model, for profilers: the prompt of 2,048 tokens, or decode steps."""
+def _engine_for(cfg, dtype, batch, max_seq, tokens=None, seed=1234):
+    from ziglm_b200 import Engine, EngineOptions, config_from_dict
+    page = 64
+    max_tokens = tokens if tokens is not None else batch * (-(-max_seq // page) * page)
+    return Engine.from_config(config_from_dict(cfg), EngineOptions(dtype=dtype, max_batch=batch, max_seq_len=max_seq,
+                                                                   max_tokens=max_tokens, seed=seed))
+
+
+def _time_prompt(eng, prompt, warmup, steps):
+    """Median device time (ms) of one prompt step of a fresh sequence."""
     import torch
-    from ziglm_b200 import Engine, EngineOptions, config_from_dict, kernels
+    times = []
+    for k in range(warmup + steps):
+        slot = eng.alloc_slot()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        eng.step([(slot, prompt)])
+        e.record()
+        torch.cuda.synchronize()
+        if k >= warmup:
+            times.append(s.elapsed_time(e))
+        eng.free_slot(slot)
+    return sorted(times)[len(times) // 2]
+
+
+def _time_decode_at(eng, batch, context, warmup, steps, ids):
+    """Median device time (ms) of a decode step of ``batch`` sequences that hold ``context`` tokens when the timed
+    steps end.  The cache is given its length without being computed: a decode step's time does not depend on
+    what the cache holds."""
+    import torch
+    slots = [eng.alloc_slot() for _ in range(batch)]
+    grow = {s: max(1, context - warmup - steps - 1) for s in slots}
+    eng.cache.slots.reserve(grow)
+    eng.cache.slots.advance(grow)
+    times = []
+    for k in range(warmup + steps):
+        toks = ids(batch)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        eng.step([(sl, [t]) for sl, t in zip(slots, toks)])
+        e.record()
+        torch.cuda.synchronize()
+        if k >= warmup:
+            times.append(s.elapsed_time(e))
+    for s in slots:
+        eng.free_slot(s)
+    return sorted(times)[len(times) // 2]
+
+
+def run_case(args):
+    """A single phase on a (possibly shallower) model, for profilers and sweeps: a prompt, or decode steps."""
+    import torch
+    from ziglm_b200 import kernels
     torch.cuda.set_device(0)
-    cfg = dict(LLAMA_8B)
-    cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
+    cfg = dict(SHAPES[args.shape])
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = args.layers or full_layers
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], args.context + 64, args.prompt_tokens + 64)
     batch, context = args.batch, args.context
     max_seq = max(context, args.prompt_tokens) + 64
-    eng = Engine.from_config(config_from_dict(cfg), EngineOptions(
-        dtype="bfloat16", max_batch=batch, max_seq_len=max_seq, max_tokens=batch * (-(-max_seq // 64) * 64), seed=1234))
+    eng = _engine_for(cfg, args.dtype, batch, max_seq)
     gen = torch.Generator().manual_seed(7)
     ids = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
-    times = []
+    pk = peaks()
+    el = 2 if args.dtype == "bfloat16" else 4
+    out = {"case": args.case, "shape": args.shape, "dtype": args.dtype, "layers": cfg["num_hidden_layers"],
+           "layers_of_config": full_layers, "batch": batch, "context": context}
     if args.case == "prefill":
-        prompt = ids(args.prompt_tokens)
-        for k in range(args.warmup + args.steps):
-            slot = eng.alloc_slot()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            s.record()
-            eng.step([(slot, prompt)])
-            e.record()
-            torch.cuda.synchronize()
-            if k >= args.warmup:
-                times.append(s.elapsed_time(e))
-            eng.free_slot(slot)
-        tokens = args.prompt_tokens
+        ms = _time_prompt(eng, ids(args.prompt_tokens), args.warmup, args.steps)
+        flops = prefill_flops(cfg, cfg["num_hidden_layers"], args.prompt_tokens)
+        out.update({"prompt_tokens": args.prompt_tokens, "ms": round(ms, 4),
+                    "tok_s": round(args.prompt_tokens / ms * 1000.0, 1), "tflops": round(flops / ms / 1e9, 1)})
+        if args.dtype == "bfloat16":
+            out["frac_of_bf16_peak"] = round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
     else:
-        slots = [eng.alloc_slot() for _ in range(batch)]
-        # the cache is given its length without being computed: a decode step's time does not depend on its content
-        grow = {s: context - args.warmup - args.steps - 1 for s in slots}
-        eng.cache.slots.reserve(grow)
-        eng.cache.slots.advance(grow)
-        for k in range(args.warmup + args.steps):
-            toks = ids(batch)
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ms = _time_decode_at(eng, batch, context, args.warmup, args.steps, ids)
+        nbytes = decode_bytes(cfg, cfg["num_hidden_layers"], batch, context, el)
+        out.update({"ms": round(ms, 4), "tok_s": round(batch / ms * 1000.0, 1), "gb_per_step": round(nbytes / 1e9, 3),
+                    "hbm_frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)})
+    out["peaks"] = pk["source"]
+    out["wait_errors"] = wait_errors(kernels)
+    print(json.dumps(out))
+    return 0
+
+
+def run_workload(args):
+    """The two workloads beside the headline one, through ``Engine.generate`` (host token ids in, ids out):
+
+    workload-1b   Llama-3.2-1B shape (tied head): 64 prompts with seeded lengths in [16, 1024] in one step of
+                  unequal lengths, then 128 decode steps;
+    workload-13b  Llama-2-13B shape (every head its own keys): 8 prompts of 2,048 tokens, then 256 decode steps.
+
+    Times are the loop's own wall-clock times (they include the copies and the read-back of every step); the
+    roofline fractions divide the bytes every decode step has to read (weights once, the live sequences' cache
+    at its length in that step) and the prompt step's FLOPs by those times and the measured peaks."""
+    import random
+    import torch
+    from ziglm_b200 import GenerationOptions, SamplerParams, kernels
+    torch.cuda.set_device(0)
+    which = "1b" if args.case == "workload-1b" else "13b"
+    cfg = dict(SHAPES[which])
+    full_layers = cfg["num_hidden_layers"]
+    n_layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = n_layers
+    if which == "1b":
+        rng = random.Random(1)
+        lens = [rng.randint(16, 1024) for _ in range(64)]
+        new = 128
+    else:
+        lens = [2048] * 8
+        new = 256
+    B = len(lens)
+    max_seq = max(lens) + new + 64
+    tokens_needed = sum(-(-(l + new + 1) // 64) * 64 for l in lens)
+    eng = _engine_for(cfg, "bfloat16", B, max_seq, tokens=tokens_needed + 64 * B, seed=5)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg["vocab_size"], (l,), generator=g).tolist() for l in lens]
+    # the first token comes from the prompt step, the other `new` from decode steps
+    opts = GenerationOptions(max_tokens=new + 1, sampler=SamplerParams(greedy=True), ignore_eos=True)
+    pk = peaks()
+    runs = []
+    with ClockSampler() as clocks:
+        for rep in range(1 + max(1, args.repeats)):
             torch.cuda.synchronize()
-            s.record()
-            eng.step([(sl, [t]) for sl, t in zip(slots, toks)])
-            e.record()
+            results, stats = eng.generate(prompts, opts)
             torch.cuda.synchronize()
-            if k >= args.warmup:
-                times.append(s.elapsed_time(e))
-        tokens = batch
-    ms = sorted(times)[len(times) // 2]
-    print(json.dumps({"case": args.case, "layers": cfg["num_hidden_layers"], "batch": batch, "context": context,
-                      "ms": round(ms, 4), "tok_s": round(tokens / ms * 1000.0, 1),
-                      "wait_errors": [kernels.gemm_tc_status(), kernels.attention_tc_status(),
-                                      kernels.attention_fmha_status()]}))
+            if rep:
+                runs.append(stats)
+    stats = sorted(runs, key=lambda st: st.generation_time_ms)[len(runs) // 2]
+    assert all(len(r.tokens) == new + 1 for r in results)
+    flops = sum(prefill_flops(cfg, n_layers, l) for l in lens)
+    step_bytes = [decode_bytes(cfg, n_layers, B, 0, cached_tokens=sum(lens) + B * (k + 1)) for k in range(new)]
+    ms_step = stats.generation_time_ms / new
+    out = {
+        "case": args.case, "model": {"1b": "Llama-3.2-1B shape", "13b": "Llama-2-13B shape"}[which], "dtype": "bf16",
+        "layers": n_layers, "layers_of_config": full_layers, "batch": B, "prompt_tokens": sum(lens),
+        "prompt_lengths": [min(lens), max(lens)], "decode_steps": new,
+        "prefill_ms": round(stats.prefill_time_ms, 2), "prefill_tok_s": round(stats.prefill_tokens_per_sec(), 1),
+        "prefill_tflop": round(flops / 1e12, 2),
+        "prefill_frac_of_bf16_peak": round(flops / (stats.prefill_time_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+        "ms_per_step": round(ms_step, 4), "decode_tok_s": round(B * new / stats.generation_time_ms * 1000.0, 1),
+        "decode_gb_per_step": [round(step_bytes[0] / 1e9, 3), round(step_bytes[-1] / 1e9, 3)],
+        "decode_hbm_frac": round(sum(step_bytes) / (stats.generation_time_ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+        "peaks": pk["source"], "clocks": clocks.summary(), "wait_errors": wait_errors(kernels),
+        "data": "synthetic: random N(0,0.02) weights, uniform random token ids; through Engine.generate, wall clock",
+    }
+    print(json.dumps(out))
+    return 0
+
+
+def run_float32(args):
+    """The 8B shape in true 32-bit (CUDA-core products and attention, float32 weights, activations and cache):
+    a prompt of 2,048 tokens and decode steps at batch 1 and 8, context 4,096."""
+    import torch
+    from ziglm_b200 import kernels
+    torch.cuda.set_device(0)
+    cfg = dict(LLAMA_8B)
+    full_layers = cfg["num_hidden_layers"]
+    n_layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = n_layers
+    max_seq = CONTEXT + 64
+    eng = _engine_for(cfg, "float32", 8, max_seq)
+    gen = torch.Generator().manual_seed(7)
+    ids = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
+    pk = peaks()
+    steps, warmup = max(3, min(args.steps, 10)), 3
+    pre_ms = _time_prompt(eng, ids(PREFILL_TOKENS), 1, 3)
+    flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+    out = {"case": "float32", "model": "Llama-3.1-8B shape", "dtype": "float32 (no tensor cores, no reduced-precision mode)",
+           "layers": n_layers, "layers_of_config": full_layers, "context": CONTEXT,
+           "prefill": {"tokens": PREFILL_TOKENS, "ms": round(pre_ms, 2), "tok_s": round(PREFILL_TOKENS / pre_ms * 1000.0, 1),
+                       "tflops": round(flops / pre_ms / 1e9, 2)}}
+    for batch in (1, 8):
+        ms = _time_decode_at(eng, batch, CONTEXT, warmup, steps, ids)
+        nbytes = decode_bytes(cfg, n_layers, batch, CONTEXT, 4)
+        out[f"decode_b{batch}"] = {"ms": round(ms, 3), "tok_s": round(batch / ms * 1000.0, 1),
+                                   "gb_per_step": round(nbytes / 1e9, 2),
+                                   "hbm_frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+    out["peaks"] = pk["source"]
+    out["wait_errors"] = wait_errors(kernels)
+    print(json.dumps(out))
     return 0
 
 
@@ -455,9 +638,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the configuration has (both numbers are reported)")
-    ap.add_argument("--case", default="full", choices=["full", "prefill", "decode", "reference-kernels"],
-                    help="full: the whole measurement; prefill / decode: that phase alone (for profilers); "
-                         "reference-kernels: the reference's CUDA kernels alone, if they were built")
+    ap.add_argument("--case", default="full",
+                    choices=["full", "prefill", "decode", "workload-1b", "workload-13b", "float32", "reference-kernels"],
+                    help="full: the whole measurement; prefill / decode: that phase alone (for profilers and sweeps); "
+                         "workload-1b / workload-13b: the two other workloads through Engine.generate; float32: the "
+                         "8B shape in true 32-bit; reference-kernels: the reference's CUDA kernels alone, if built")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="--case prefill/decode: layer sizes")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="--case prefill/decode")
+    ap.add_argument("--repeats", type=int, default=2, help="workload cases: timed repetitions after one warm-up")
     ap.add_argument("--batch", type=int, default=8, help="--case decode: sequences in the batch")
     ap.add_argument("--context", type=int, default=CONTEXT, help="--case decode: tokens each sequence holds")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="--case prefill: tokens of the prompt")
@@ -472,6 +660,10 @@ def main():
         return 2
     if args.case == "reference-kernels":
         return run_reference_kernels(args)
+    if args.case in ("workload-1b", "workload-13b"):
+        return run_workload(args)
+    if args.case == "float32":
+        return run_float32(args)
     if args.case != "full":
         return run_case(args)
     return run_ours(args)
