@@ -115,6 +115,31 @@ def test_gemm_generic(K, xd, wd, yd, M, N, K_):
         assert torch.allclose(acc.cpu(), base + P.linear(x.float(), w), atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("N,K_", [(130, 64), (33, 1000), (4100, 520), (31, 4), (256, 4096)])
+def test_few_tokens_in_float32_take_the_streaming_kernel_and_keep_the_order_of_the_sums(K, M, N, K_):
+    """Float operands with at most 32 tokens run a kernel of their own (32 weight rows a block, a thread per
+    row and token).  It adds every output's products in ascending k like the tiled kernel, so the rows of a
+    step of few tokens equal, bit for bit, the same rows computed inside a step of many tokens."""
+    x, w, b = rnd((M, K_), torch.float32, seed=5), rnd((N, K_), torch.float32, seed=6), rnd((N,), torch.float32, seed=7)
+    out = torch.full((M, N), 9.0, device=DEV)
+    K.gemm_generic(x.to(DEV), w.to(DEV), out, bias=b.to(DEV))
+    assert torch.allclose(out.cpu(), P.linear(x, w, b), atol=1e-5 * max(1.0, K_ ** 0.5), rtol=1e-5)
+    # the same rows as the first M of 70 tokens (the tiled kernel)
+    many = torch.cat([x, rnd((70 - M, K_), torch.float32, seed=8)])
+    out_many = torch.empty(70, N, device=DEV)
+    K.gemm_generic(many.to(DEV), w.to(DEV), out_many, bias=b.to(DEV))
+    assert torch.equal(out, out_many[:M])
+    # accumulating into rows of a wider buffer, inputs that are rows of a wider buffer
+    wide_x = torch.zeros(M, K_ + 8, device=DEV)
+    wide_x[:, 4:4 + K_] = x.to(DEV)
+    wide_y = torch.full((M, N + 5), 2.0, device=DEV)
+    K.gemm_generic(wide_x[:, 4:4 + K_], w.to(DEV), wide_y[:, :N], accumulate=True)
+    ref = torch.full((70, N), 2.0, device=DEV)
+    K.gemm_generic(many.to(DEV), w.to(DEV), ref, accumulate=True)
+    assert torch.equal(wide_y[:, :N], ref[:M]) and (wide_y[:, N:] == 2.0).all()
+
+
 def test_gemm_generic_strided_rows_and_true_float32(K):
     """Rows of a wider buffer; and float32 products are not rounded to a shorter mantissa."""
     buf = rnd((10, 100), torch.float32, seed=9).to(DEV)
@@ -231,6 +256,44 @@ def test_attention_general(K, dtype, nh, nkv, hd, window):
                         torch.tensor(seq, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV), vp.to(DEV), 64)
     want = plain_attention_rows(ks, vs, q, positions, seq, scale, window)
     assert torch.allclose(out.float().cpu().reshape(T, nh, hd), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (6, 3, 48), (3, 3, 64), (16, 2, 256)])
+@pytest.mark.parametrize("window", [None, 300])
+def test_attention_general_over_many_keys_whole_and_in_parts(K, dtype, nh, nkv, hd, window):
+    """Sequences of up to 1,100 keys (several parts of 256): the kernel that folds all parts of a token itself and
+    the split run (a block per part, folded by a second kernel) agree bit for bit, and both with the plain rows."""
+    lens_past, lens_new = [1099, 255, 256, 700, 3], [1, 1, 1, 1, 1]
+    ks, vs, q, positions, seq = dense_attention_case(dtype, nh, nkv, hd, lens_past, lens_new, seed=33)
+    kp, vp, table = paged(ks, vs, 64, dtype, seed=4)
+    T = q.shape[0]
+    scale = 1.0 / math.sqrt(hd)
+    args = (nh, nkv, hd, scale, window, torch.tensor(positions, dtype=torch.int32, device=DEV),
+            torch.tensor(seq, dtype=torch.int32, device=DEV), table.to(DEV), kp.to(DEV), vp.to(DEV), 64)
+    qd = q.reshape(T, nh * hd).to(DEV)
+    whole = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    K.attention_general(qd, whole, *args)
+    max_keys = min(1100, window or 1100)
+    need = K.attention_general_scratch(T, nh, nkv, hd, max_keys)
+    assert need > 0
+    scratch = torch.full((need + 7,), float("nan"), device=DEV)
+    parts = torch.empty_like(whole)
+    K.attention_general(qd, parts, *args, max_keys=max_keys, scratch=scratch)
+    assert torch.equal(parts, whole)
+    # a bound on the keys that is larger than any sequence (a captured step knows only the cache's limit)
+    need_big = K.attention_general_scratch(T, nh, nkv, hd, 4096)
+    scratch = torch.full((need_big,), float("nan"), device=DEV)
+    parts.zero_()
+    K.attention_general(qd, parts, *args, max_keys=4096, scratch=scratch)
+    assert torch.equal(parts, whole)
+    want = plain_attention_rows(ks, vs, q, positions, seq, scale, window)
+    assert torch.allclose(whole.float().cpu().reshape(T, nh, hd), want, **tol(dtype))
+    # many tokens need no scratch, and too little scratch is not used
+    assert K.attention_general_scratch(400, nh, nkv, hd, 1100) == 0 and K.attention_general_scratch(T, nh, nkv, hd, 200) == 0
+    parts.zero_()
+    K.attention_general(qd, parts, *args, max_keys=max_keys, scratch=torch.empty(8, device=DEV))
+    assert torch.equal(parts, whole)
 
 
 def test_attention_refuses_head_sizes_it_cannot_run(K):

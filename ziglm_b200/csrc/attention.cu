@@ -185,130 +185,264 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_
 }
 
 // ------------------------------------------------------------ attention
-// grid (T, n_heads); 128 threads.  Warp w takes the key blocks w, w+4, ... of 32
-// keys; lane j scores key j of the block, then the lanes split the head's
-// dimensions for the weighted sum of values.  The four partial results are
-// merged in warp order, so the result depends only on (start, pos).
+// The keys a token sees, [start, pos], are cut into parts of ATT_PART = 256 consecutive keys counted from
+// `start`.  Within a part warp w of a block takes the key blocks w and w + 4 of 32 keys: lane j scores key j of
+// a block, then the lanes split the head's dimensions for the weighted sum of values; the four warps' partial
+// results are merged in warp order into the part's (max, sum, weighted values).  The parts are then folded one
+// after another, in ascending order, into the result.  A block works for G query heads that share a key/value
+// head (the largest of 4, 2, 1 that divides the group), so a key or value row is read once for all of them.
+//
+// Two ways to run, with bit-for-bit the same result, because a part's result depends on (start, pos, part)
+// alone and the fold is the same arithmetic in the same order:
+//   whole   grid (T, n_heads / G, 1): a block computes and folds all parts of its token (prompts: the tokens
+//           alone give enough blocks);
+//   split   grid (T, n_heads / G, parts): a block computes one part and stores it in scratch memory, and
+//           attention_fold_kernel folds a token's parts (steps of few tokens: the parts give the blocks).
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_MAX_HD = 256;
+constexpr int ATT_PART = ATT_WARPS * 2 * 32;
 
-template <typename T, int VEC>
-__device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int hd);
-
-template <>
-__device__ __forceinline__ float dot_row<float, 4>(const float* __restrict__ q, const float* __restrict__ k, int hd) {
-    float acc = 0.f;
-    for (int d = 0; d < hd; d += 4) {
-        const float4 kv = *reinterpret_cast<const float4*>(k + d);
-        acc = fmaf(q[d], kv.x, acc);
-        acc = fmaf(q[d + 1], kv.y, acc);
-        acc = fmaf(q[d + 2], kv.z, acc);
-        acc = fmaf(q[d + 3], kv.w, acc);
-    }
-    return acc;
+// k[d..d+VEC) of one key row as floats
+template <typename T, int VEC> __device__ __forceinline__ void load_vec(const T* __restrict__ p, float (&f)[VEC]);
+template <> __device__ __forceinline__ void load_vec<float, 4>(const float* __restrict__ p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
 }
-
-template <>
-__device__ __forceinline__ float dot_row<__nv_bfloat16, 8>(const float* __restrict__ q,
-                                                           const __nv_bfloat16* __restrict__ k, int hd) {
-    float acc = 0.f;
-    for (int d = 0; d < hd; d += 8) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(k + d);
-        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+template <> __device__ __forceinline__ void load_vec<__nv_bfloat16, 8>(const __nv_bfloat16* __restrict__ p, float (&f)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(p[i]);
-            acc = fmaf(q[d + 2 * i], f.x, acc);
-            acc = fmaf(q[d + 2 * i + 1], f.y, acc);
-        }
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(h[i]);
+        f[2 * i] = v.x; f[2 * i + 1] = v.y;
     }
-    return acc;
 }
 
-template <typename T, int VEC>
+// Fold a part (mp, lp, op) into the running (m, l, o): every operation is one rounded multiply, add or fused
+// multiply-add, written out so that both kernels that fold do exactly the same.
+__device__ __forceinline__ void fold_weights(float m, float mp, float& m_new, float& a, float& b) {
+    m_new = fmaxf(m, mp);
+    a = expf(m - m_new);                 // exp(-inf) = 0 for the first part
+    b = expf(mp - m_new);
+}
+__device__ __forceinline__ float fold_value(float o, float a, float op, float b) {
+    return __fmaf_rn(op, b, __fmul_rn(o, a));
+}
+
+template <typename T, int VEC, int G, int NREG>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restrict__ out, int n_heads, int n_kv,
                          int hd, float scale, int window, const int* __restrict__ positions,
                          const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int bt_stride,
                          const T* __restrict__ k_pages, const T* __restrict__ v_pages, int page_size,
-                         long page_stride) {
-    __shared__ float q_s[ATT_MAX_HD];
-    __shared__ float acc_s[ATT_WARPS][ATT_MAX_HD];
-    __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
+                         long page_stride, float* __restrict__ part_ml, float* __restrict__ part_o, int max_parts) {
+    __shared__ float q_s[G][ATT_MAX_HD];
+    __shared__ float acc_s[G][ATT_WARPS][NREG * 32];
+    __shared__ float m_s[G][ATT_WARPS], l_s[G][ATT_WARPS];
 
-    const int t = blockIdx.x, h = blockIdx.y;
+    const int t = blockIdx.x, h0 = blockIdx.y * G;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos = positions[t];
     const int b = seq_of_token[t];
-    const int kvh = h / (n_heads / n_kv);
+    const int kvh = h0 / (n_heads / n_kv);
     const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int n_keys = pos - start + 1;
+    const int n_parts = (n_keys + ATT_PART - 1) / ATT_PART;
+    const bool split = part_o != nullptr;
+    const int p_lo = split ? (int)blockIdx.z : 0, p_hi = split ? min(n_parts, (int)blockIdx.z + 1) : n_parts;
+    if (p_lo >= n_parts) return;
     const int* bt = block_table + (long)b * bt_stride;
 
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) q_s[i] = to_float(q[(long)t * q_row_stride + (long)h * hd + i]);
+    for (int i = threadIdx.x; i < G * hd; i += blockDim.x)
+        q_s[i / hd][i % hd] = to_float(q[(long)t * q_row_stride + (long)(h0 + i / hd) * hd + i % hd]);
     __syncthreads();
 
-    constexpr int NREG = ATT_MAX_HD / 32;
-    float acc[NREG];
+    // the running result: thread x owns dimensions x and x + 128 of every head
+    float run_m[G], run_l[G], run_o[G][2];
 #pragma unroll
-    for (int i = 0; i < NREG; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    for (int g = 0; g < G; ++g) { run_m[g] = -INFINITY; run_l[g] = 0.f; run_o[g][0] = run_o[g][1] = 0.f; }
 
-    const int n_keys = pos - start + 1;
-    const int n_blocks = (n_keys + 31) / 32;
-    for (int kb = warp; kb < n_blocks; kb += ATT_WARPS) {
-        const int j = start + kb * 32 + lane;
-        const bool valid = j <= pos;
-        float s = -INFINITY;
-        long row_off = 0;
-        if (valid) {
-            const int page = bt[j / page_size];
-            row_off = (long)page * page_stride + ((long)kvh * page_size + j % page_size) * hd;
-            s = dot_row<T, VEC>(q_s, k_pages + row_off, hd) * scale;
+    for (int part = p_lo; part < p_hi; ++part) {
+        float acc[G][NREG], m[G], l[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+            for (int i = 0; i < NREG; ++i) acc[g][i] = 0.f;
         }
-        const float m_new = fmaxf(m, warp_max(s));       // lane 0 of the block is always valid
-        const float corr = expf(m - m_new);               // exp(-inf) = 0 on the first block
-        const float p = valid ? expf(s - m_new) : 0.f;
-        l = l * corr + warp_sum(p);
-        m = m_new;
+        const int part_first = start + part * ATT_PART;
+#pragma unroll 1
+        for (int kb = warp; kb < 2 * ATT_WARPS; kb += ATT_WARPS) {
+            const int first = part_first + kb * 32;
+            if (first > pos) break;                              // uniform per warp
+            const int j = first + lane;
+            const bool valid = j <= pos;
+            float sc[G];
 #pragma unroll
-        for (int i = 0; i < NREG; ++i) acc[i] *= corr;
-        const int n_valid = min(32, pos - (start + kb * 32) + 1);
-        for (int jj = 0; jj < n_valid; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const long voff = __shfl_sync(0xffffffffu, row_off, jj);
-            const T* vrow = v_pages + voff;
+            for (int g = 0; g < G; ++g) sc[g] = 0.f;
+            long row_off = 0;
+            if (valid) {
+                const int page = bt[j / page_size];
+                row_off = (long)page * page_stride + ((long)kvh * page_size + j % page_size) * hd;
+                const T* krow = k_pages + row_off;
+                for (int d = 0; d < hd; d += VEC) {
+                    float kv[VEC];
+                    load_vec<T, VEC>(krow + d, kv);
 #pragma unroll
-            for (int i = 0; i < NREG; ++i) {
-                const int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(pj, to_float(vrow[d]), acc[i]);
+                    for (int g = 0; g < G; ++g)
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) sc[g] = fmaf(q_s[g][d + i], kv[i], sc[g]);
+                }
+            }
+            float pr[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float sv = valid ? sc[g] * scale : -INFINITY;
+                const float m_new = fmaxf(m[g], warp_max(sv));   // lane 0 of the block is always valid
+                const float corr = expf(m[g] - m_new);           // exp(-inf) = 0 on the first block
+                pr[g] = valid ? expf(sv - m_new) : 0.f;
+                l[g] = l[g] * corr + warp_sum(pr[g]);
+                m[g] = m_new;
+#pragma unroll
+                for (int i = 0; i < NREG; ++i) acc[g][i] *= corr;
+            }
+            const int n_valid = min(32, pos - first + 1);
+            for (int jj = 0; jj < n_valid; ++jj) {
+                const long voff = __shfl_sync(0xffffffffu, row_off, jj);
+                const T* vrow = v_pages + voff;
+                float pj[G];
+#pragma unroll
+                for (int g = 0; g < G; ++g) pj[g] = __shfl_sync(0xffffffffu, pr[g], jj);
+#pragma unroll
+                for (int i = 0; i < NREG; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < hd) {
+                        const float v = to_float(vrow[d]);
+#pragma unroll
+                        for (int g = 0; g < G; ++g) acc[g][i] = fmaf(pj[g], v, acc[g][i]);
+                    }
+                }
+            }
+        }
+        __syncthreads();                                         // the part before has been folded
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (lane == 0) { m_s[g][warp] = m[g]; l_s[g][warp] = l[g]; }
+#pragma unroll
+            for (int i = 0; i < NREG; ++i) acc_s[g][warp][lane + 32 * i] = acc[g][i];
+        }
+        __syncthreads();
+        // the four warps' results, merged in warp order: the part's (max, sum, weighted values)
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float big = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < ATT_WARPS; ++w) big = fmaxf(big, m_s[g][w]);
+            float wgt[ATT_WARPS];
+            float lp = 0.f;
+#pragma unroll
+            for (int w = 0; w < ATT_WARPS; ++w) {
+                wgt[w] = m_s[g][w] == -INFINITY ? 0.f : expf(m_s[g][w] - big);
+                lp = __fmaf_rn(l_s[g][w], wgt[w], lp);
+            }
+            float a, bb, m_new;
+            fold_weights(run_m[g], big, m_new, a, bb);
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int d = threadIdx.x + r * ATT_WARPS * 32;
+                if (d < hd) {
+                    float op = 0.f;
+#pragma unroll
+                    for (int w = 0; w < ATT_WARPS; ++w) op = __fmaf_rn(acc_s[g][w][d], wgt[w], op);
+                    if (split) part_o[(((long)t * n_heads + h0 + g) * max_parts + part) * hd + d] = op;
+                    else run_o[g][r] = fold_value(run_o[g][r], a, op, bb);
+                }
+            }
+            if (split) {
+                if (threadIdx.x == 0) {
+                    float* ml = part_ml + (((long)t * n_heads + h0 + g) * max_parts + part) * 2;
+                    ml[0] = big; ml[1] = lp;
+                }
+            } else {
+                run_l[g] = fold_value(run_l[g], a, lp, bb);
+                run_m[g] = m_new;
             }
         }
     }
+    if (split) return;
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int d = threadIdx.x + r * ATT_WARPS * 32;
+            if (d < hd) out[((long)t * n_heads + h0 + g) * hd + d] = from_float<T>(run_o[g][r] / run_l[g]);
+        }
+}
 
-    if (lane == 0) { m_s[warp] = m; l_s[warp] = l; }
+// grid (T, n_heads), 128 threads: folds the parts a split launch left in scratch memory, in ascending order.
+template <typename T>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, const int* __restrict__ positions,
+                      const float* __restrict__ part_ml, const float* __restrict__ part_o, int max_parts) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int pos = positions[t];
+    const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int n_parts = (pos - start + 1 + ATT_PART - 1) / ATT_PART;
+    const float* ml = part_ml + ((long)t * n_heads + h) * max_parts * 2;
+    const float* po = part_o + ((long)t * n_heads + h) * max_parts * hd;
+    float run_m = -INFINITY, run_l = 0.f, run_o[2] = {0.f, 0.f};
+    for (int part = 0; part < n_parts; ++part) {
+        float a, bb, m_new;
+        fold_weights(run_m, ml[2 * part], m_new, a, bb);
 #pragma unroll
-    for (int i = 0; i < NREG; ++i) {
-        const int d = lane + 32 * i;
-        if (d < hd) acc_s[warp][d] = acc[i];
+        for (int r = 0; r < 2; ++r) {
+            const int d = threadIdx.x + r * ATT_WARPS * 32;
+            if (d < hd) run_o[r] = fold_value(run_o[r], a, po[(long)part * hd + d], bb);
+        }
+        run_l = fold_value(run_l, a, ml[2 * part + 1], bb);
+        run_m = m_new;
     }
-    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int d = threadIdx.x + r * ATT_WARPS * 32;
+        if (d < hd) out[((long)t * n_heads + h) * hd + d] = from_float<T>(run_o[r] / run_l);
+    }
+}
 
-    float big = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) big = fmaxf(big, m_s[w]);
-    float wgt[ATT_WARPS];
-    float denom = 0.f;
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) {
-        wgt[w] = m_s[w] == -INFINITY ? 0.f : expf(m_s[w] - big);
-        denom += l_s[w] * wgt[w];
-    }
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float o = 0.f;
-#pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) o += acc_s[w][d] * wgt[w];
-        out[((long)t * n_heads + h) * hd + d] = from_float<T>(o / denom);
-    }
+template <typename T, int VEC, int G>
+static int launch_attention(const void* q, long q_row_stride, void* out, int T_, int n_heads, int n_kv, int hd, float scale,
+                            int window, const int* positions, const int* seq_of_token, const int* block_table,
+                            int bt_stride, const void* k_pages, const void* v_pages, int page_size, long page_stride,
+                            float* part_ml, float* part_o, int max_parts, cudaStream_t stream) {
+    dim3 grid(T_, n_heads / G, part_o ? max_parts : 1);
+    if (hd <= 128)
+        attention_general_kernel<T, VEC, G, 4><<<grid, ATT_WARPS * 32, 0, stream>>>(
+            (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, window, positions, seq_of_token, block_table,
+            bt_stride, (const T*)k_pages, (const T*)v_pages, page_size, page_stride, part_ml, part_o, max_parts);
+    else
+        attention_general_kernel<T, VEC, G, 8><<<grid, ATT_WARPS * 32, 0, stream>>>(
+            (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, window, positions, seq_of_token, block_table,
+            bt_stride, (const T*)k_pages, (const T*)v_pages, page_size, page_stride, part_ml, part_o, max_parts);
+    int rc = launch_status();
+    if (rc || !part_o) return rc;
+    attention_fold_kernel<T><<<dim3(T_, n_heads), ATT_WARPS * 32, 0, stream>>>((T*)out, n_heads, hd, window, positions,
+                                                                           part_ml, part_o, max_parts);
+    return launch_status();
+}
+
+template <typename T, int VEC>
+static int pick_group(int group, const void* q, long q_row_stride, void* out, int T_, int n_heads, int n_kv, int hd,
+                      float scale, int window, const int* positions, const int* seq_of_token, const int* block_table,
+                      int bt_stride, const void* k_pages, const void* v_pages, int page_size, long page_stride,
+                      float* part_ml, float* part_o, int max_parts, cudaStream_t stream) {
+#define ZLM_ATT(GV)                                                                                                     \
+    launch_attention<T, VEC, GV>(q, q_row_stride, out, T_, n_heads, n_kv, hd, scale, window, positions, seq_of_token,   \
+                                 block_table, bt_stride, k_pages, v_pages, page_size, page_stride, part_ml, part_o,     \
+                                 max_parts, stream)
+    if (group % 4 == 0) return ZLM_ATT(4);
+    if (group % 2 == 0) return ZLM_ATT(2);
+    return ZLM_ATT(1);
+#undef ZLM_ATT
 }
 
 }  // namespace zlm
@@ -355,25 +489,44 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
+// Floats of scratch memory that let zlm_attention_general spread a step of T tokens whose longest visible range
+// is max_keys keys over more blocks (0: the step has enough tokens, or one part of keys).
+ZLM_EXPORT long zlm_attention_general_scratch(int T, int n_heads, int n_kv, int hd, int max_keys) {
+    if (T <= 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return 0;
+    const int group = n_heads / n_kv, g = group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+    const long parts = (max_keys + ATT_PART - 1) / ATT_PART;
+    if (parts <= 1 || (long)T * (n_heads / g) >= 2 * 148) return 0;
+    return (long)T * n_heads * parts * (hd + 2);
+}
+
+// max_keys: the most keys any token of the step sees.  scratch (float, scratch_floats elements; may be null):
+// when it holds at least zlm_attention_general_scratch(...) floats and that is not 0, the parts of the keys are
+// computed by blocks of their own and folded by a second kernel; the result is bit for bit the same.
 ZLM_EXPORT int zlm_attention_general(const void* q, long q_row_stride, void* out, int dtype, int T, int n_heads,
                                      int n_kv, int hd, float scale, int window, const int* positions,
                                      const int* seq_of_token, const int* block_table, int bt_stride,
                                      const void* k_pages, const void* v_pages, int page_size, long page_stride,
-                                     cudaStream_t stream) {
+                                     int max_keys, float* scratch, long scratch_floats, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0) return ZLM_ERR_BAD_ARG;
     if (hd <= 0 || hd > ATT_MAX_HD || hd % 8) return ZLM_ERR_UNSUPPORTED;
-    dim3 grid(T, n_heads);
+    float *part_ml = nullptr, *part_o = nullptr;
+    int max_parts = 1;
+    const long need = zlm_attention_general_scratch(T, n_heads, n_kv, hd, max_keys);
+    if (need > 0 && scratch != nullptr && scratch_floats >= need) {
+        max_parts = (max_keys + ATT_PART - 1) / ATT_PART;
+        if (max_parts > 65535) return ZLM_ERR_UNSUPPORTED;
+        part_o = scratch;
+        part_ml = scratch + (long)T * n_heads * max_parts * hd;
+    }
+    const int group = n_heads / n_kv;
     if (dtype == ZLM_F32)
-        attention_general_kernel<float, 4><<<grid, ATT_WARPS * 32, 0, stream>>>(
-            (const float*)q, q_row_stride, (float*)out, n_heads, n_kv, hd, scale, window, positions, seq_of_token,
-            block_table, bt_stride, (const float*)k_pages, (const float*)v_pages, page_size, page_stride);
-    else if (dtype == ZLM_BF16)
-        attention_general_kernel<__nv_bfloat16, 8><<<grid, ATT_WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, n_heads, n_kv, hd, scale, window, positions,
-            seq_of_token, block_table, bt_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
-            page_size, page_stride);
-    else
-        return ZLM_ERR_UNSUPPORTED;
-    return launch_status();
+        return pick_group<float, 4>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, window, positions,
+                                    seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size, page_stride,
+                                    part_ml, part_o, max_parts, stream);
+    if (dtype == ZLM_BF16)
+        return pick_group<__nv_bfloat16, 8>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, window, positions,
+                                            seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size,
+                                            page_stride, part_ml, part_o, max_parts, stream);
+    return ZLM_ERR_UNSUPPORTED;
 }

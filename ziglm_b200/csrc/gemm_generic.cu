@@ -10,6 +10,12 @@
 // Each output element is owned by one thread that adds its K products in
 // ascending k with fmaf, so a value does not depend on M, on where the row sits
 // in the batch, or on the tile it falls in.
+//
+// Two kernels keep that rule.  gemm_generic_kernel tiles 64 tokens x 64 weight
+// rows; a step of a few tokens would use a sixty-fourth of such a tile and too few
+// blocks to draw on the memory system, so float operands with at most 32 tokens go
+// to gemm_skinny_kernel, which streams 32 weight rows a block through a ring of
+// asynchronous copies and gives every (row, token) pair to one thread.
 #include "common.cuh"
 
 namespace zlm {
@@ -84,6 +90,146 @@ gemm_generic_kernel(const TX* __restrict__ X, const TW* __restrict__ W, const TB
     }
 }
 
+// ------------------------------------------------------ few tokens, float operands
+// A block owns SK_ROWS weight rows and all M <= 4 * TT tokens.  Lane l of every warp owns row l; warp w owns the
+// tokens w * TT .. w * TT + TT - 1, so a thread carries TT running sums.  The K range comes in chunks of SK_BK
+// floats: all threads issue 16-byte asynchronous copies of the rows' chunk and of the tokens' chunk into one
+// of SK_STAGES stages, and compute from the oldest stage while the younger ones are in flight.  A row of a
+// stage is padded by four floats, so that the 32 lanes' 16-byte reads of their rows fall in different banks.
+constexpr int SK_ROWS = 32, SK_WARPS = 4, SK_BK = 128, SK_STAGES = 4, SK_LD = SK_BK + 4;
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, int src_bytes) {
+    // copies src_bytes (0..16) and fills the rest of the 16 bytes with zeros
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int TT, typename TB, bool ACC>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+gemm_skinny_kernel(const float* __restrict__ X, const float* __restrict__ W, const TB* __restrict__ bias,
+                   float* __restrict__ Y, int M, int N, int K, long ldx, long ldw, long ldy) {
+    constexpr int TOK = SK_WARPS * TT;                       // token rows staged
+    extern __shared__ __align__(16) float sk_smem[];
+    float* Ws = sk_smem;                                     // [SK_STAGES][SK_ROWS][SK_LD]
+    float* Xs = sk_smem + SK_STAGES * SK_ROWS * SK_LD;       // [SK_STAGES][TOK][SK_LD]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * SK_ROWS;
+    const int n_chunks = (K + SK_BK - 1) / SK_BK;
+
+    auto issue = [&](int chunk) {
+        const int stage = chunk % SK_STAGES, k0 = chunk * SK_BK;
+        float* ws = Ws + stage * SK_ROWS * SK_LD;
+        float* xs = Xs + stage * TOK * SK_LD;
+        // a row's chunk is SK_BK / 4 pieces of 16 bytes; pieces beyond K are zeros
+        for (int i = tid; i < SK_ROWS * (SK_BK / 4); i += SK_WARPS * 32) {
+            const int r = i / (SK_BK / 4), c = (i % (SK_BK / 4)) * 4;
+            const int gr = min(n0 + r, N - 1);               // rows beyond N repeat the last one and are not stored
+            const int left = (K - (k0 + c)) * 4;
+            cp_async_16(ws + r * SK_LD + c, W + (long)gr * ldw + k0 + (left > 0 ? c : 0), left >= 16 ? 16 : (left > 0 ? left : 0));
+        }
+        for (int i = tid; i < TOK * (SK_BK / 4); i += SK_WARPS * 32) {
+            const int r = i / (SK_BK / 4), c = (i % (SK_BK / 4)) * 4;
+            const int gr = min(r, M - 1);
+            const int left = (K - (k0 + c)) * 4;
+            cp_async_16(xs + r * SK_LD + c, X + (long)gr * ldx + k0 + (left > 0 ? c : 0), left >= 16 ? 16 : (left > 0 ? left : 0));
+        }
+    };
+
+    for (int c = 0; c < SK_STAGES - 1; ++c) {
+        if (c < n_chunks) issue(c);
+        cp_async_commit();
+    }
+    float acc[TT];
+#pragma unroll
+    for (int t = 0; t < TT; ++t) acc[t] = 0.f;
+    const bool active = warp * TT < M;                       // warps whose tokens do not exist only help copying
+
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        cp_async_wait<SK_STAGES - 2>();                      // this thread's copies of the oldest stage have landed
+        __syncthreads();                                     // ... and everyone's; the stage computed last is free
+        if (chunk + SK_STAGES - 1 < n_chunks) issue(chunk + SK_STAGES - 1);
+        cp_async_commit();
+        if (active) {
+            const float* ws = Ws + (chunk % SK_STAGES) * SK_ROWS * SK_LD + lane * SK_LD;
+            const float* xs = Xs + (chunk % SK_STAGES) * TOK * SK_LD + warp * TT * SK_LD;
+#pragma unroll 4
+            for (int k = 0; k < SK_BK; k += 4) {
+                const float4 w = *reinterpret_cast<const float4*>(ws + k);
+#pragma unroll
+                for (int t = 0; t < TT; ++t) {
+                    const float4 x = *reinterpret_cast<const float4*>(xs + t * SK_LD + k);
+                    // ascending k, one fused multiply-add each: the order of gemm_generic_kernel
+                    acc[t] = fmaf(x.x, w.x, acc[t]);
+                    acc[t] = fmaf(x.y, w.y, acc[t]);
+                    acc[t] = fmaf(x.z, w.z, acc[t]);
+                    acc[t] = fmaf(x.w, w.w, acc[t]);
+                }
+            }
+        }
+    }
+    const int gn = n0 + lane;
+    if (!active || gn >= N) return;
+    const float b = bias ? to_float(bias[gn]) : 0.f;
+#pragma unroll
+    for (int t = 0; t < TT; ++t) {
+        const int gm = warp * TT + t;
+        if (gm >= M) break;
+        float v = acc[t];
+        if (bias) v += b;
+        float* dst = Y + (long)gm * ldy + gn;
+        if (ACC) *dst = *dst + v;
+        else *dst = v;
+    }
+}
+
+template <int TT, typename TB, bool ACC>
+static int launch_skinny_one(const float* X, const float* W, const void* bias, float* Y, int M, int N, int K, long ldx,
+                             long ldw, long ldy, cudaStream_t stream) {
+    const int smem = SK_STAGES * (SK_ROWS + SK_WARPS * TT) * SK_LD * (int)sizeof(float);
+    static bool configured = false;                          // one flag per kernel: this function is its only launcher
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<TT, TB, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_skinny_kernel<TT, TB, ACC><<<(N + SK_ROWS - 1) / SK_ROWS, SK_WARPS * 32, smem, stream>>>(
+        X, W, (const TB*)bias, Y, M, N, K, ldx, ldw, ldy);
+    return launch_status();
+}
+
+template <int TT, typename TB>
+static int launch_skinny_tt(const float* X, const float* W, const void* bias, float* Y, int accumulate, int M, int N,
+                            int K, long ldx, long ldw, long ldy, cudaStream_t stream) {
+    if (accumulate) return launch_skinny_one<TT, TB, true>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, stream);
+    return launch_skinny_one<TT, TB, false>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, stream);
+}
+
+// Float operands whose rows start on 16-byte boundaries, at most 32 tokens.  Returns ZLM_ERR_UNSUPPORTED otherwise.
+static int launch_skinny(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int accumulate, int M,
+                         int N, int K, long ldx, long ldw, long ldy, cudaStream_t stream) {
+    if (M > 8 * SK_WARPS || (K & 3) || (ldx & 3) || (ldw & 3) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        return ZLM_ERR_UNSUPPORTED;
+    if (bias != nullptr && bias_dtype != ZLM_F32 && bias_dtype != ZLM_BF16) return ZLM_ERR_UNSUPPORTED;
+    const int tt = (M + SK_WARPS - 1) / SK_WARPS;            // tokens per warp: 1, 2, 4 or 8
+    const float* x = (const float*)X;
+    const float* w = (const float*)W;
+    float* y = (float*)Y;
+#define ZLM_SKINNY(TTV)                                                                                              \
+    (bias != nullptr && bias_dtype == ZLM_BF16                                                                       \
+         ? launch_skinny_tt<TTV, __nv_bfloat16>(x, w, bias, y, accumulate, M, N, K, ldx, ldw, ldy, stream)             \
+         : launch_skinny_tt<TTV, float>(x, w, bias, y, accumulate, M, N, K, ldx, ldw, ldy, stream))
+    if (tt <= 1) return ZLM_SKINNY(1);
+    if (tt <= 2) return ZLM_SKINNY(2);
+    if (tt <= 4) return ZLM_SKINNY(4);
+    return ZLM_SKINNY(8);
+#undef ZLM_SKINNY
+}
+
 template <typename TX, typename TW, typename TY, typename TB>
 static int launch(const void* X, const void* W, const void* bias, void* Y, int accumulate, int M, int N, int K,
                   long ldx, long ldw, long ldy, cudaStream_t stream) {
@@ -128,6 +274,10 @@ ZLM_EXPORT int zlm_gemm_generic(const void* X, int x_dtype, const void* W, int w
                                 long ldx, long ldw, long ldy, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || ldx < K || ldw < K || ldy < N) return ZLM_ERR_BAD_ARG;
+    if (x_dtype == ZLM_F32 && w_dtype == ZLM_F32 && y_dtype == ZLM_F32 && M <= 8 * SK_WARPS) {
+        const int rc = launch_skinny(X, W, bias, bias_dtype, Y, accumulate, M, N, K, ldx, ldw, ldy, stream);
+        if (rc != ZLM_ERR_UNSUPPORTED) return rc;
+    }
     if (x_dtype == ZLM_F32 && w_dtype == ZLM_F32)
         return pick_y<float, float>(y_dtype, bias_dtype, X, W, bias, Y, accumulate, M, N, K, ldx, ldw, ldy, stream);
     if (x_dtype == ZLM_F32 && w_dtype == ZLM_BF16)

@@ -65,7 +65,9 @@ _PROTOTYPES = {
         "zlm_rope_store": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
         "zlm_attention_general": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
+                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_int,
+                                  c_void_p, c_long, c_void_p],
+        "zlm_attention_general_scratch": [c_int, c_int, c_int, c_int, c_int],
     },
     "attention_tc": {
         "zlm_attention_decode": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
@@ -281,13 +283,22 @@ def rope_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary
         _ptr(k_pages), _ptr(v_pages), page_size, page_stride, _stream()), "rope_store")
 
 
+def attention_general_scratch(n_tokens: int, n_heads: int, n_kv: int, head_dim: int, max_keys: int) -> int:
+    """Floats of scratch with which ``attention_general`` spreads a step of few tokens over more blocks (0: none
+    is of use)."""
+    return int(_fn("attention", "zlm_attention_general_scratch")(n_tokens, n_heads, n_kv, head_dim, max_keys))
+
+
 def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
                       window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                       block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
-                      page_size: int) -> None:
+                      page_size: int, max_keys: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
     """out[t, h, :] = softmax(q[t,h] . K[start..pos_t] * scale) @ V over the paged cache.
 
     The queries are the first n_heads*head_dim columns of each row of ``qkv`` (any row stride).
+    ``max_keys`` (the most keys a token of the step sees) and ``scratch`` (float32, at least
+    ``attention_general_scratch(...)`` elements) let a step of few tokens use more blocks; the result does not
+    depend on them.
     """
     _cuda(out, "out", qkv.dtype); _cuda(k_pages, "k_pages", qkv.dtype); _cuda(v_pages, "v_pages", qkv.dtype)
     _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
@@ -304,8 +315,13 @@ def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: 
     _check(_fn("attention", "zlm_attention_general")(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), code(qkv.dtype), T, n_heads, n_kv, head_dim, scale,
         int(window or 0), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
-        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), page_size, k_pages.stride(0), _stream()),
+        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), page_size, k_pages.stride(0), int(max_keys),
+        _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream()),
         "attention_general")
+    if scratch is not None and max_keys > 0 and scratch.numel() >= attention_general_scratch(
+            T, n_heads, n_kv, head_dim, max_keys) > 0:
+        global _launches
+        _launches += 1          # the fold of the parts is a second launch
 
 
 def _tc_attention_ok(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
@@ -548,8 +564,11 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
                 return
             if attention_prefill(*args):
                 return
+    max_keys = min(step.max_total, window) if window else step.max_total
+    need = attention_general_scratch(step.n_tokens, n_heads, n_kv, head_dim, max_keys)
+    scratch = step.ws.buf("attn_parts", (need,), torch.float32) if need > 0 else None
     attention_general(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
-                      io.block_table, io.k_pages, io.v_pages, io.page_size)
+                      io.block_table, io.k_pages, io.v_pages, io.page_size, max_keys, scratch)
 
 
 def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1, n_kv: int = 1):
