@@ -251,9 +251,38 @@ def test_a_batch_that_shrinks_through_many_sizes_generates_what_each_request_gen
                 row = logits[len(p) - 1 + k]
                 slack = 2 * (tol["atol"] + tol["rtol"] * row.max().abs().item())
                 assert row[tok].item() >= row.max().item() - slack, f"request {i}, token {k}"
-    # what the graphs of all batch sizes hold beside the model
-    held = sum(g.ws.bytes() for g in eng._graphs.values())
-    assert held < 64 * 1024 * 1024, f"decode graphs hold {held} bytes of scratch"
+    # the captured steps of all batch sizes share one workspace: its size is that of the largest batch
+    assert all(g.ws is eng.graph_ws for g in eng._graphs.values())
+    assert eng.graph_ws.bytes() < 8 * 1024 * 1024, f"decode graphs hold {eng.graph_ws.bytes()} bytes of scratch"
+
+
+@pytest.mark.parametrize("dn", ["float32", "bfloat16"])
+def test_a_larger_batch_after_a_smaller_one_moves_the_shared_scratch_and_every_size_stays_right(zoo, dn):
+    """Decode steps of one sequence are captured first; then four sequences decode together, which makes the
+    shared scratch of the captured steps grow and move; then one sequence decodes again.  Its captured launches
+    point to memory that is gone, so they are captured anew, and every step's logits match the plain model."""
+    folder, eng = zoo.get("D", dn, max_batch=4, max_tokens=1024, seed=5)
+    V = helpers.CONFIGS["D"]["vocab_size"]
+    act = None if dn == "float32" else torch.bfloat16
+    reqs = [helpers.random_tokens(40, V, 900 + i) for i in range(4)]
+    want = [helpers.plain_logits(folder, r, act=act) for r in reqs]
+    slots = [eng.alloc_slot() for _ in reqs]
+    eng.step([(slots[0], reqs[0][:10])], [[]])
+    rows0 = [eng.step([(slots[0], [reqs[0][k]])]).clone() for k in range(10, 14)]          # size 1 is captured
+    first_graph = eng._graphs[1].graph
+    moves = eng.graph_ws.moves
+    eng.step([(s, r[:20]) for s, r in zip(slots[1:], reqs[1:])], [[], [], []])
+    eng.step([(slots[0], reqs[0][14:20])], [[]])
+    rows_all = [eng.step([(s, [r[k]]) for s, r in zip(slots, reqs)]).clone() for k in range(20, 26)]   # size 4
+    assert eng.graph_ws.moves > moves
+    rows0b = [eng.step([(slots[0], [reqs[0][k]])]).clone() for k in range(26, 32)]         # size 1 again
+    assert eng._graphs[1].graph is not first_graph
+    helpers.assert_close(torch.cat(rows0), want[0][10:14], DTYPES[dn], "one sequence, first capture")
+    for i in range(4):
+        helpers.assert_close(torch.stack([r[i] for r in rows_all]), want[i][20:26], DTYPES[dn], f"four sequences, {i}")
+    helpers.assert_close(torch.cat(rows0b), want[0][26:32], DTYPES[dn], "one sequence, captured anew")
+    for s in slots:
+        eng.free_slot(s)
 
 
 def test_wanted_places_and_nothing_wanted(zoo):

@@ -90,6 +90,7 @@ class Engine:
         kv, reads, state = model.cache_plan()
         self.cache = CacheStorage(kv, reads, state, max_tokens, n_slots, self.max_seq_len, self.dtype, self.device)
         self.ws = Workspace(self.device)
+        self.graph_ws = Workspace(self.device)     # scratch of the captured decode steps, shared by all batch sizes
         self._host = [None, None]
         self._host_events = [None, None]
         self._dev: Optional[torch.Tensor] = None
@@ -327,7 +328,7 @@ class Engine:
         if not any(codes.values()):
             return
         self._repeat = None
-        for ws in [self.ws] + [g.ws for g in self._graphs.values()]:
+        for ws in (self.ws, self.graph_ws):
             ws.zero("attn_flat_counters")
         raise kernels.KernelError("a bounded wait ran out inside a kernel, the step's results are not valid: "
                                   + kernels.describe_wait_errors(codes))
@@ -405,7 +406,8 @@ class _DecodeGraph:
         self.events = [torch.cuda.Event(), torch.cuda.Event()]
         self.used = [False, False]
         self.flip = 0
-        self.ws = Workspace(engine.device)
+        self.ws = engine.graph_ws               # shared: steps run one after another, and so do replays
+        self.ws_moves = -1                      # ``ws.moves`` when the launches were captured
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.kernels_per_replay = 0
@@ -433,11 +435,13 @@ class _DecodeGraph:
 
     def run(self, past: List[int], slots: List[int]) -> torch.Tensor:
         e = self.engine
-        if self.graph is not None:
+        if self.graph is not None and self.ws_moves == self.ws.moves:
             self.graph.replay()
             e._graph_kernels += self.kernels_per_replay
             return self.logits
-        # first step of this batch size: run it as it is (this also sizes the scratch), then capture it
+        # First step of this batch size, or a larger batch has since made the shared scratch grow and move: run
+        # the step as it is (this also sizes the scratch), then capture it.
+        self.graph = None
         step = self._context(past, slots)
         before = kernels.launches()
         logits = e.model.forward(step)
@@ -457,5 +461,5 @@ class _DecodeGraph:
                 gc.enable()
         kernels.reset_launches_by(self.kernels_per_replay)
         assert captured.data_ptr() == logits.data_ptr()
-        self.graph, self.logits = graph, logits
+        self.graph, self.logits, self.ws_moves = graph, logits, self.ws.moves
         return logits

@@ -2,8 +2,11 @@
 
 Layers run one after another and ask for the same names, so a step's scratch is
 as large as its largest layer needs.  A buffer grows when a larger request
-comes; an engine that has captured CUDA graphs gives each graph a workspace of
-its own, so that growth elsewhere never moves memory a graph still points to.
+comes, and growing moves it: ``moves`` counts how often that has happened, so
+that whoever recorded addresses of this workspace (captured CUDA graphs) can tell
+that they are stale.  The captured decode steps of all batch sizes share one
+workspace of their own, apart from the one of prompt steps, whose growth would
+otherwise move what they point to.
 """
 from __future__ import annotations
 
@@ -16,6 +19,7 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._flat: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self.moves = 0
 
     def buf(self, name: str, shape, dtype: torch.dtype, zeros: bool = False) -> torch.Tensor:
         """The named buffer, at least as large as ``shape``.  ``zeros``: the memory is zero when it is first
@@ -26,6 +30,8 @@ class Workspace:
         key = (name, dtype)
         flat = self._flat.get(key)
         if flat is None or flat.numel() < n:
+            if flat is not None:
+                self.moves += 1                 # a buffer someone may point to is replaced
             make = torch.zeros if zeros else torch.empty
             flat = make(max(n, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
