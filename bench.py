@@ -35,34 +35,9 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LLAMA_8B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
-    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
-    "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                     "original_max_position_embeddings": 8192},
-    "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
-    "attention_bias": False,
-}
-LLAMA_1B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16,
-    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256,
-    "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                     "original_max_position_embeddings": 8192},
-    "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
-    "attention_bias": False,
-}
-LLAMA_13B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
-    "hidden_size": 5120, "intermediate_size": 13824, "num_hidden_layers": 40,
-    "num_attention_heads": 40, "num_key_value_heads": 40, "head_dim": 128, "vocab_size": 32000,
-    "rope_theta": 10000.0, "rope_scaling": None,
-    "max_position_embeddings": 4096, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
-    "attention_bias": False,
-}
+from ziglm_b200.config.shapes import shape as _shape  # noqa: E402  (plain dictionaries, no CUDA needed)
+
+LLAMA_8B, LLAMA_1B, LLAMA_13B = _shape("llama-8b"), _shape("llama-1b"), _shape("llama-13b")
 SHAPES = {"8b": LLAMA_8B, "1b": LLAMA_1B, "13b": LLAMA_13B}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048

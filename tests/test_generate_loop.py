@@ -176,15 +176,11 @@ def test_engine_check_names_the_code_and_repairs_the_counters():
         def __init__(self): self.zeroed = []
         def zero(self, name): self.zeroed.append(name)
 
-    class Graph:
-        def __init__(self): self.ws = Buf()
-
     e = Engine.__new__(Engine)
-    e.ws, e._graphs, e._repeat = Buf(), {4: Graph(), 2: Graph()}, object()
+    e.ws, e.graph_ws, e._repeat = Buf(), Buf(), object()
     e.check_kernels(read=lambda: {"gemm_tc": 0, "attention_tc": 0})
     assert e._repeat is not None and e.ws.zeroed == []
     with pytest.raises(KernelError) as err:
         e.check_kernels(read=lambda: {"gemm_tc": 0, "attention_tc": 11})
     assert "attention_tc" in str(err.value) and "11" in str(err.value) and "page" in str(err.value)
-    assert e._repeat is None and e.ws.zeroed == ["attn_flat_counters"]
-    assert all(g.ws.zeroed == ["attn_flat_counters"] for g in e._graphs.values())
+    assert e._repeat is None and e.ws.zeroed == ["attn_flat_counters"] and e.graph_ws.zeroed == ["attn_flat_counters"]

@@ -192,3 +192,18 @@ def test_command_line(models, tmp_path):
     r = subprocess.run([sys.executable, exe, "run", "-m", sample, "-p", "1 2 3", "-n", "3", "--greedy", "--device", "cpu"],
                        capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode != 0 and "no CPU path" in r.stderr
+    # a model filled from a seed, a random prompt, a stop token of the user's: the run ends at it and does not print it
+    base = [sys.executable, exe, "run", "-m", "synthetic:tiny", "--random-prompt", "9", "-n", "12", "--greedy",
+            "--dtype", "float32", "--seed", "4"]
+    r = subprocess.run(base, capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr
+    ids = [int(t) for t in r.stdout.split()]
+    assert len(ids) == 12
+    r = subprocess.run(base + ["--stop-ids", str(ids[5])], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and [int(t) for t in r.stdout.split()] == ids[:ids.index(ids[5])], r.stderr
+    r = subprocess.run([sys.executable, exe, "bench", "-m", "synthetic:llama-1b", "--layers", "1", "-n", "3", "--batch", "3",
+                        "--prompt-len", "40"], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and r.stdout.count("Iteration") == 3, r.stderr
+    r = subprocess.run([sys.executable, exe, "run", "-m", "synthetic:nothing", "-p", "1"], capture_output=True, text=True,
+                       env=env, timeout=300)
+    assert r.returncode != 0 and "not a known shape" in r.stderr

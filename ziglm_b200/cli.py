@@ -1,8 +1,11 @@
 """The command line, in the manner of the reference's (src/cli.zig).
 
     ziglm run   -m <model_folder> -p "<token ids>" -n <N> [--greedy | -t T --top-k K --top-p P --min-p M --seed S]
-    ziglm bench -m <model_folder> [-n N]
+    ziglm bench -m <model_folder> [-n N] [--batch B] [--prompt-len L]
     ziglm test-model --create-sample <folder>
+
+``-m synthetic:<shape>`` (tiny, llama-1b, llama-8b, llama-13b, or the path of a config.json) runs a model whose
+weights are filled from ``--seed`` on the device, with no folder (``--layers L`` keeps the first L layers).
 
 Option names, defaults and meanings are the reference's (src/cli.zig:67-149): ``-m/--model``,
 ``-p/--prompt``, ``-n/--max-tokens`` (256), ``--max-seq-len`` (4096), ``--echo-prompt``, ``-t/--temp`` (0.7),
@@ -12,7 +15,9 @@ Option names, defaults and meanings are the reference's (src/cli.zig:67-149): ``
 commas or blanks instead of text, and generated ids are printed instead of text.  ``run`` samples with a
 repetition penalty of 1.1 unless greedy, and prints prefill and generation speed as the reference does
 (src/cli.zig:292-334); ``bench`` runs one prompt three times greedily and prints a line per iteration
-(src/cli.zig:439-469).  ``chat``, ``serve`` and ``info`` belong to the reference's tokenizer, server and GGUF
+(src/cli.zig:439-469); with ``--batch B`` it generates for B prompts of ``--prompt-len`` random ids together.
+``--random-prompt LEN`` stands for a prompt of LEN random ids, ``--stop-ids`` adds stop tokens to the model's
+(the reference's ``stop_tokens`` option, src/engine.zig:475-482).  ``chat``, ``serve`` and ``info`` belong to the reference's tokenizer, server and GGUF
 reader and do not exist here.
 """
 from __future__ import annotations
@@ -52,6 +57,12 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="precision of the run")
     p.add_argument("--max-batch", type=int, default=8, help="most sequences generated together")
     p.add_argument("--ignore-eos", action="store_true", help="do not stop at the model's end-of-sequence ids")
+    p.add_argument("--random-prompt", type=int, default=None, metavar="LEN",
+                   help="a prompt of LEN token ids drawn from --seed instead of -p")
+    p.add_argument("--stop-ids", default=None, help="token ids that end a sequence, beside the model's own")
+    p.add_argument("--layers", type=int, default=None, help="synthetic models: keep the first L layers")
+    p.add_argument("--batch", type=int, default=1, help="bench: prompts generated together (default: 1)")
+    p.add_argument("--prompt-len", type=int, default=20, help="bench: random ids per prompt (default: 20)")
     p.add_argument("--create-sample", dest="sample_out", default="sample_model",
                    help="test-model: folder the sample model is written to")
     return p
@@ -62,13 +73,33 @@ def _engine(args):
     if args.device.lower() == "cpu":
         raise SystemExit("--device cpu: this library has no CPU path")
     if not args.model_path:
-        raise SystemExit("a model folder is needed (-m <path>)")
+        raise SystemExit("a model is needed (-m <folder> or -m synthetic:<shape>)")
     print(f"Loading model: {args.model_path} ...", file=sys.stderr)
-    from .config import read_config_json
-    limit = int(read_config_json(args.model_path).get("max_position_embeddings") or args.max_seq_len)
+    from .config import SHAPES, read_config_json, shape
+    synthetic = args.model_path.startswith("synthetic:")
+    if synthetic:
+        name = args.model_path[len("synthetic:"):]
+        if name in SHAPES:
+            cfg = shape(name)
+        elif name.endswith(".json"):
+            import json
+            with open(name) as f:
+                cfg = json.load(f)
+        else:
+            raise SystemExit(f"synthetic:{name}: not a known shape ({', '.join(sorted(SHAPES))}) nor a config.json")
+        if args.layers:
+            cfg["num_hidden_layers"] = min(args.layers, cfg["num_hidden_layers"])
+    else:
+        cfg = read_config_json(args.model_path)
+    limit = int(cfg.get("max_position_embeddings") or args.max_seq_len)
     opts = EngineOptions(num_threads=args.threads, max_seq_len=min(args.max_seq_len, limit), seed=args.seed,
-                         use_gpu=True, dtype=args.dtype, max_batch=args.max_batch)
-    return Engine.load(args.model_path, opts)
+                         use_gpu=True, dtype=args.dtype, max_batch=max(args.max_batch, getattr(args, "batch", 1)))
+    return Engine.from_config(cfg, opts) if synthetic else Engine.load(args.model_path, opts)
+
+
+def _random_prompt(engine, n: int, seed: int) -> List[int]:
+    rng = random.Random(seed)
+    return [rng.randrange(engine.vocab_size) for _ in range(n)]
 
 
 def _print_stats(stats) -> None:
@@ -90,14 +121,16 @@ def run(args) -> int:
             prompts = [_ids(line) for line in f if line.strip()]
     elif args.prompt is not None:
         prompts = [_ids(args.prompt)]
+    elif args.random_prompt:
+        prompts = [_random_prompt(engine, args.random_prompt, args.seed)]
     else:
-        raise SystemExit("a prompt is needed (-p \"<token ids>\" or --prompt-file <file>)")
+        raise SystemExit("a prompt is needed (-p \"<token ids>\", --prompt-file <file> or --random-prompt LEN)")
     greedy = args.greedy or args.temperature <= 0.0
     sampler = SamplerParams(temperature=0.0 if greedy else args.temperature, top_p=args.top_p, top_k=args.top_k,
                             min_p=args.min_p, seed=args.seed, greedy=greedy,
                             repetition_penalty=1.0 if greedy else 1.1)       # src/cli.zig:302-315
     options = GenerationOptions(max_tokens=args.max_tokens, sampler=sampler, echo_prompt=args.echo_prompt,
-                                ignore_eos=args.ignore_eos)
+                                ignore_eos=args.ignore_eos, stop_tokens=_ids(args.stop_ids) if args.stop_ids else ())
     print(f"\nPrompt: {' '.join(str(t) for t in prompts[0])}" + (f" (+{len(prompts) - 1} more)" if len(prompts) > 1 else "")
           + "\n", file=sys.stderr)
     results, stats = engine.generate(prompts, options)
@@ -113,15 +146,16 @@ def bench(args) -> int:
     engine = _engine(args)
     print(f"Running benchmark on: {args.model_path} ...", file=sys.stderr)
     if args.prompt is not None:
-        prompt = _ids(args.prompt)
+        prompts = [_ids(args.prompt)] * args.batch
     else:
-        rng = random.Random(args.seed)
-        prompt = [rng.randrange(engine.vocab_size) for _ in range(20)]     # the reference's prompt has about 20 words
+        # the reference's prompt has about 20 words; every sequence of a batch gets ids of its own
+        n = args.random_prompt or args.prompt_len
+        prompts = [_random_prompt(engine, n, args.seed + b) for b in range(args.batch)]
     options = GenerationOptions(max_tokens=args.max_tokens, ignore_eos=True,
                                 sampler=SamplerParams(greedy=True, temperature=0.0, repetition_penalty=1.0))
     print("Running 3 warmup & benchmark iterations ...", file=sys.stderr)
     for it in range(3):
-        _, stats = engine.generate([prompt], options)
+        _, stats = engine.generate(prompts, options)
         print(f"  Iteration {it + 1}: Prefill = {stats.prefill_tokens_per_sec():.1f} tok/s | Generation = "
               f"{stats.generation_tokens_per_sec():.1f} tok/s | Total = {stats.total_time_ms:.1f} ms")
     return 0
