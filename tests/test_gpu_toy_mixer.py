@@ -263,3 +263,108 @@ def test_a_layer_may_read_another_layers_cache(toy, tmp_path):
     s = eng.alloc_slot()
     rows = [eng.step([(s, toks[:25])], [list(range(25))]).clone()] + [eng.step([(s, [t])]).clone() for t in toks[25:]]
     helpers.assert_close(torch.cat(rows), want, torch.float32, "shared cache")
+
+
+def test_an_arrangement_with_options_and_hooks_behind_the_embedding_and_the_head(toy):
+    """A block kind that lives in this test reads a further norm from ``LayerSpec.options`` and applies it after
+    the mixer (a post-norm); a hook adds learned absolute positions to the embedded tokens and another one a
+    bias and a soft cap to the logits.  All three are registered from here; no file of the library changes."""
+    from ziglm_b200.config.spec import (FeedForwardSpec, HookSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec)
+    from ziglm_b200.engine.engine import Engine, EngineOptions
+    from ziglm_b200.engine.model import Model, declare_parameters
+    from ziglm_b200.parts import (ParamDecl, Part, block_class, norm_class, register_block, register_hook, unregister)
+    from ziglm_b200.weights import random_tensors
+    PreNorm = block_class("prenorm")
+
+    class PostNormBlock(PreNorm):
+        """x += post(mixer(norm(x))); x += ffn(norm(x)): the mixer's output goes through a norm of its own."""
+
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            post = spec.options["post_mixer_norm"]
+            self.post = norm_class(post.kind)(post, dtype, device)
+            self.gain = float(spec.options["mixer_gain"])
+
+        @classmethod
+        def declare(cls, spec):
+            out = dict(super().declare(spec))
+            post = spec.options["post_mixer_norm"]
+            for name, decl in norm_class(post.kind).declare(post).items():
+                out["post_mixer_norm." + name] = decl
+            return out
+
+        def bind(self, tensors):
+            super().bind(tensors)
+            self.post.bind({k[len("post_mixer_norm."):]: v for k, v in tensors.items() if k.startswith("post_mixer_norm.")})
+
+        def accepts_normed_input(self):
+            return False
+
+        def forward(self, step, io, x, h_in=None, next_norm=None):
+            h = self.mixer_norm.forward(step, x)
+            branch = torch.zeros_like(x)
+            self.mixer.forward(step, io, h, branch)
+            x += self.post.forward(step, branch, name="post_out").float() * self.gain
+            self.ffn.forward(step, self.ffn_norm.forward(step, x), x)
+            return None
+
+    class LearnedPositions(Part):
+        @classmethod
+        def declare(cls, spec):
+            return {"table": ParamDecl((spec.options["max_positions"], spec.options["width"]))}
+
+        def bind(self, tensors):
+            self.table = tensors["table"]
+
+        def forward(self, step, x):
+            x += self.table.float().index_select(0, step.positions.long())
+
+    class BiasAndCap(Part):
+        @classmethod
+        def declare(cls, spec):
+            return {"bias": ParamDecl((spec.options["vocab_size"],))}
+
+        def bind(self, tensors):
+            self.bias = tensors["bias"]
+
+        def forward(self, step, logits):
+            cap = float(self.spec.options["cap"])
+            logits.copy_(torch.tanh((logits + self.bias.float()) / cap) * cap)
+
+    register_block("toy_postnorm", PostNormBlock)
+    register_hook("toy_learned_positions", LearnedPositions)
+    register_hook("toy_bias_and_cap", BiasAndCap)
+    try:
+        d, V = 32, 61
+        norm = NormSpec("rmsnorm", d, 1e-5)
+        att = MixerSpec(kind="attention", width=d, n_heads=2, n_kv_heads=1, head_dim=16)
+        layer = LayerSpec("toy_postnorm", "l0.", norm, att, norm, FeedForwardSpec("gated_mlp", d, 40),
+                          options={"post_mixer_norm": NormSpec("rmsnorm", d, 1e-6), "mixer_gain": 0.5})
+        spec = ModelSpec("Hooked", d, V, (layer,), (0,), norm, "embed", "norm", "head", max_positions=128,
+                         embed_hook=HookSpec("toy_learned_positions", {"max_positions": 128, "width": d}, {"table": "positions.table"}),
+                         logits_hook=HookSpec("toy_bias_and_cap", {"vocab_size": V, "cap": 2.0}, {"bias": "head.bias"}))
+        decl = declare_parameters(spec)
+        assert {"positions.table", "head.bias", "l0.post_mixer_norm.weight"} <= set(decl)
+        dev = torch.device("cuda:0")
+        w = dict(random_tensors(decl, 4, torch.float32, dev, std=0.2, norm_jitter=0.1))
+        model = Model(spec, torch.float32, dev)
+        model.bind(w)
+        eng = Engine(None, model, EngineOptions(dtype="float32", max_tokens=256, max_batch=2, max_seq_len=128))
+        toks = helpers.random_tokens(30, V, 6)
+        T = len(toks)
+        w = {k: v.cpu() for k, v in w.items()}
+        x = P.embedding(toks, w["embed"]) + w["positions.table"][:T]
+        h = P.rms_norm(x, w["l0.mixer_norm.weight"], 1e-5)
+        q = P.linear(h, w["l0.mixer.q.weight"]).view(T, 2, 16)
+        k = P.linear(h, w["l0.mixer.k.weight"]).view(T, 1, 16)
+        v = P.linear(h, w["l0.mixer.v.weight"]).view(T, 1, 16)
+        branch = P.linear(P.attention(q, k, v, 0.25).reshape(T, 32), w["l0.mixer.o.weight"])
+        x = x + 0.5 * P.rms_norm(branch, w["l0.post_mixer_norm.weight"], 1e-6)
+        h = P.rms_norm(x, w["l0.ffn_norm.weight"], 1e-5)
+        x = x + P.swiglu(h, w["l0.ffn.gate.weight"], w["l0.ffn.up.weight"], w["l0.ffn.down.weight"], None)
+        want = torch.tanh((P.linear(P.rms_norm(x, w["norm"], 1e-5), w["head"]) + w["head.bias"]) / 2.0) * 2.0
+        s = eng.alloc_slot()
+        rows = [eng.step([(s, toks[:11])], [list(range(11))]).clone()] + [eng.step([(s, [t])]).clone() for t in toks[11:]]
+        helpers.assert_close(torch.cat(rows), want, torch.float32, "post-norm block with hooks")
+    finally:
+        unregister("block", "toy_postnorm"); unregister("hook", "toy_learned_positions"); unregister("hook", "toy_bias_and_cap")
