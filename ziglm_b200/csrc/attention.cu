@@ -285,6 +285,8 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
                 const int page = bt[j / page_size];
                 row_off = (long)page * page_stride + ((long)kvh * page_size + j % page_size) * hd;
                 const T* krow = k_pages + row_off;
+                // several 16-byte loads of the row in flight at once: the loop is bound by their latency
+#pragma unroll 8
                 for (int d = 0; d < hd; d += VEC) {
                     float kv[VEC];
                     load_vec<T, VEC>(krow + d, kv);
@@ -307,6 +309,7 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
                 for (int i = 0; i < NREG; ++i) acc[g][i] *= corr;
             }
             const int n_valid = min(32, pos - first + 1);
+#pragma unroll 4
             for (int jj = 0; jj < n_valid; ++jj) {
                 const long voff = __shfl_sync(0xffffffffu, row_off, jj);
                 const T* vrow = v_pages + voff;
