@@ -251,7 +251,9 @@ def sample(logits: torch.Tensor, u: float, temperature: float, top_k: int, top_p
     """The reference's order (src/sampler.zig:78-157): logits/T, softmax, sort by probability (descending; ties by
     lower id), keep k, cut below min_p * p_max (keeping at least one), cut after the cumulative probability reaches
     top_p, then draw r = u * sum(kept) and take the first kept candidate whose running sum is >= r.  With no top_k
-    the candidates stay in id order (the draw's distribution is the same)."""
+    the candidates stay in id order (the draw's distribution is the same); top_p then keeps the same set as the
+    sorted chain would (the shortest prefix by descending probability, ties by lower id, whose probability
+    reaches top_p; the running probability is summed exactly, in units of 2^-44)."""
     z = logits.to(torch.float32) * torch.tensor(1.0 / temperature, dtype=torch.float32)
     e = torch.exp(z - z.max())
     prob = e / e.sum()
@@ -277,6 +279,16 @@ def sample(logits: torch.Tensor, u: float, temperature: float, top_k: int, top_p
         if min_p > 0.0:
             thresh = prob.max() * torch.tensor(min_p, dtype=torch.float32)
             ids = [i for i in ids if prob[i] >= thresh]
+        if top_p < 1.0:
+            unit = float(2 ** 44)
+            want = int(float(torch.tensor(top_p, dtype=torch.float32)) * unit)
+            cum, kept = 0, set()
+            for i in sorted(ids, key=lambda i: (-prob[i].item(), i)):
+                kept.add(i)
+                cum += int(float(prob[i]) * unit)
+                if cum >= want:
+                    break
+            ids = [i for i in ids if i in kept]
     total = torch.tensor(0.0, dtype=torch.float32)
     for i in ids:
         total = total + prob[i]

@@ -393,7 +393,8 @@ def test_argmax(K):
 
 
 @pytest.mark.parametrize("temperature,top_k,top_p,min_p", [(0.7, 40, 0.9, 0.05), (1.0, 0, 1.0, 0.0), (1.3, 5, 1.0, 0.0),
-                                                           (0.5, 0, 1.0, 0.1), (1.0, 1000, 0.95, 0.0)])
+                                                           (0.5, 0, 1.0, 0.1), (1.0, 1000, 0.95, 0.0),
+                                                           (1.0, 0, 0.9, 0.0), (0.6, 0, 0.5, 0.02), (2.5, 0, 0.97, 0.0)])
 def test_sample_follows_the_chain(K, temperature, top_k, top_p, min_p):
     from ziglm_b200.sampling import uniform01
     V, rows = 331, 48
@@ -457,12 +458,45 @@ def test_sample_penalties(K):
     assert torch.allclose(d.cpu()[0], want)
 
 
+def test_top_p_without_top_k_keeps_the_nucleus_of_the_sorted_chain(K):
+    """top_p with no top_k: the kept set is the shortest prefix by descending probability that reaches top_p, also
+    when that takes more candidates than any top_k this library sorts (a flat row of a wide vocabulary), with
+    equal logits at the edge taken in id order; nothing outside the set is ever drawn."""
+    from ziglm_b200.sampling import uniform01
+    V = 50021
+    g = torch.Generator().manual_seed(21)
+    flat = torch.randn(V, generator=g) * 0.3                           # the nucleus of 0.9 holds tens of thousands
+    peaked = torch.randn(V, generator=g) * 4.0
+    ties = torch.zeros(V)
+    ties[100:140] = 5.0                                                # 40 equal logits: top_p cuts among them
+    rows = torch.stack([flat, peaked, ties])
+    for top_p in (0.9, 0.3):
+        prob = torch.softmax(rows, -1)
+        for r in range(3):
+            order = sorted(range(V), key=lambda i: (-prob[r, i].item(), i))
+            cum, nucleus = 0.0, set()
+            for i in order:
+                nucleus.add(i); cum += prob[r, i].item()
+                if cum >= top_p:
+                    break
+            picks = set()
+            for c in range(24):
+                rng = torch.tensor([[77 + r, c]], dtype=torch.int64, device=DEV)
+                out = torch.empty(1, dtype=torch.int32, device=DEV)
+                K.sample(rows[r:r + 1].to(DEV), out, rng, 1.0, 0, top_p, 0.0)
+                want = P.sample(rows[r], uniform01(77 + r, c), 1.0, 0, top_p, 0.0)
+                # the draw is a running sum over the kept ids: over tens of thousands of equal probabilities (the
+                # third row) the device's order of additions may end one id away from the sequential sum
+                assert out.item() == want if r < 2 else abs(out.item() - want) <= 2
+                picks.add(out.item())
+            # a float boundary may move the set's edge by one id; nothing far outside is drawn
+            assert len(picks - nucleus) <= 1 and len(picks) > 1
+
+
 def test_sample_refuses_what_it_cannot_do(K):
     l = torch.zeros(1, 10, device=DEV)
     o = torch.empty(1, dtype=torch.int32, device=DEV)
     r = torch.zeros(1, 2, dtype=torch.int64, device=DEV)
-    with pytest.raises(K.KernelError, match="top_k"):
-        K.sample(l, o, r, 1.0, 0, 0.9, 0.0)
     with pytest.raises(K.KernelError, match="1024"):
         K.sample(l, o, r, 1.0, 5000, 1.0, 0.0)
     with pytest.raises(K.KernelError, match="temperature"):

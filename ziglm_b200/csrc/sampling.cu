@@ -14,7 +14,11 @@
 //     id ascending) and cut and drawn from in that order by one thread, in the same
 //     float operations as the plain statement of the chain.
 //   * with top_k == 0 the candidates stay in id order: min_p is a threshold, the
-//     draw is a running sum over ids.  top_p < 1 needs top_k and is refused without.
+//     draw is a running sum over ids.  top_p < 1 keeps the reference's nucleus (the
+//     shortest prefix, by descending probability and ascending id, whose probability
+//     reaches top_p): the scaled logit of its last member is found by a radix select
+//     over probability mass, summed in 2^-44 fixed point so that the sums do not depend
+//     on the order of the additions.
 // The uniform number of a draw is a pure function of (seed, counter) of the row, so
 // a sequence draws the same whatever else is in its batch.
 #include "common.cuh"
@@ -228,10 +232,81 @@ sample_kernel(float* __restrict__ logits, int V, long row_stride, SampleArgs a, 
     if (a.top_k <= 0) {
         // candidates in id order; min_p is a threshold on the probability
         const float thresh = a.min_p > 0.f ? (1.0f / denom) * a.min_p : -1.f;
+        // top_p < 1: the nucleus.  kth = key of the scaled logit of its last member; every id with a larger key
+        // is in, of the ids with that key the first tie_keep in id order.  (All keys pass when top_p is 1.)
+        unsigned kth = 0u;
+        int tie_keep = 0x7fffffff;
+        if (a.top_p < 1.0f) {
+            __shared__ unsigned long long mass[256];     // probability mass per bucket of a pass, in units of 2^-44
+            const double one = 17592186044416.0;                                            // 2^44
+            const unsigned long long want = (unsigned long long)((double)a.top_p * one);
+            __shared__ unsigned long long above_s;       // mass of the ids above the prefix found so far
+            __shared__ int found_s;                      // the nucleus ends inside the eligible ids
+            if (tid == 0) { prefix_s = 0u; above_s = 0ull; found_s = 1; }
+            __syncthreads();
+            for (int pass = 0; pass < 4 && found_s; ++pass) {
+                const int shift = 24 - 8 * pass;
+                if (tid < 256) mass[tid] = 0ull;
+                __syncthreads();
+                const unsigned prefix = prefix_s;
+                const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+                for (int i = tid; i < V; i += SAMPLE_THREADS) {
+                    const float z = row[i] * a.inv_temperature;
+                    const unsigned key = orderable(z);
+                    if ((key & mask) != prefix) continue;
+                    const float pr = expf(z - m) / denom;
+                    if (pr >= thresh) atomicAdd(&mass[(key >> shift) & 0xff], (unsigned long long)((double)pr * one));
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    unsigned long long cum = above_s;
+                    int b = 255;
+                    for (; b >= 0; --b) {
+                        if (cum + mass[b] >= want) break;
+                        cum += mass[b];
+                    }
+                    if (b < 0) found_s = 0;              // even all eligible ids stay below top_p: all are kept
+                    else { prefix_s = prefix | ((unsigned)b << shift); above_s = cum; }
+                }
+                __syncthreads();
+            }
+            if (found_s) {
+                kth = prefix_s;
+                // ids with the key kth have the same probability: as many of them as it takes to reach top_p
+                const float z_k = [&] {
+                    const unsigned u = (kth & 0x80000000u) ? (kth & 0x7fffffffu) : ~kth;
+                    return __uint_as_float(u);
+                }();
+                const unsigned long long each = (unsigned long long)((double)(expf(z_k - m) / denom) * one);
+                const unsigned long long need = want > above_s ? want - above_s : 0ull;
+                tie_keep = each > 0ull ? (int)min((unsigned long long)0x7fffffff, (need + each - 1ull) / each) : 0x7fffffff;
+                if (tie_keep < 1) tie_keep = 1;
+            }
+            __syncthreads();
+        }
+        // rank of this thread's first tie among the ties of the row, in id order
+        int my_ties = 0;
+        if (tie_keep != 0x7fffffff)
+            for (int i = lo; i < hi; ++i) {
+                const float z = row[i] * a.inv_temperature;
+                if (orderable(z) == kth && expf(z - m) / denom >= thresh) ++my_ties;
+            }
+        int tie_rank = tie_keep != 0x7fffffff ? block_exclusive_scan(my_ties, iscratch, &itotal) : 0;
+        __syncthreads();
+        const int tie_rank0 = tie_rank;
+        auto kept_prob = [&](int i, int& rank) -> float {
+            const float z = row[i] * a.inv_temperature;
+            const float pr = expf(z - m) / denom;
+            if (!(pr >= thresh)) return -1.f;
+            const unsigned key = orderable(z);
+            if (key > kth) return pr;
+            if (key == kth) return rank++ < tie_keep ? pr : -1.f;
+            return -1.f;
+        };
         float kept = 0.f;
         for (int i = lo; i < hi; ++i) {
-            const float p = expf(row[i] * a.inv_temperature - m) / denom;
-            if (p >= thresh) kept += p;
+            const float pr = kept_prob(i, tie_rank);
+            if (pr >= 0.f) kept += pr;
         }
         const float before = block_exclusive_scan_f(kept, fscratch, &ftotal);
         const float r = u * ftotal;
@@ -240,11 +315,12 @@ sample_kernel(float* __restrict__ logits, int V, long row_stride, SampleArgs a, 
         __syncthreads();
         int found = -1, last_kept = -1;
         float run = before;
+        tie_rank = tie_rank0;
         for (int i = lo; i < hi; ++i) {
-            const float p = expf(row[i] * a.inv_temperature - m) / denom;
-            if (p >= thresh) {
+            const float pr = kept_prob(i, tie_rank);
+            if (pr >= 0.f) {
                 last_kept = i;
-                run += p;
+                run += pr;
                 if (found < 0 && r <= run) found = i;
             }
         }
@@ -633,7 +709,6 @@ ZLM_EXPORT int zlm_sample(float* logits, int rows, int V, long row_stride, float
     if (V <= 0 || row_stride < V || !(temperature > 0.f) || top_k < 0 || window < 0 || window > SAMPLE_THREADS)
         return ZLM_ERR_BAD_ARG;
     if (top_k > MAX_TOP_K) return ZLM_ERR_UNSUPPORTED;
-    if (top_k == 0 && top_p < 1.0f) return ZLM_ERR_UNSUPPORTED;
     SampleArgs a;
     a.inv_temperature = 1.0f / temperature;
     a.top_k = top_k;

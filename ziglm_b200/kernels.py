@@ -739,8 +739,6 @@ def sample(logits: torch.Tensor, out: torch.Tensor, rng: torch.Tensor, temperatu
         raise KernelError("sample: the temperature must be positive (use argmax for greedy)")
     if top_k > 1024:
         raise KernelError("sample: top_k above 1024 is not supported")
-    if top_k == 0 and top_p < 1.0:
-        raise KernelError("sample: top_p below 1 needs a top_k between 1 and 1024")
     window = 0
     if history is not None:
         _cuda(history, "history", torch.int32)
