@@ -184,3 +184,110 @@ def test_engine_check_names_the_code_and_repairs_the_counters():
         e.check_kernels(read=lambda: {"gemm_tc": 0, "attention_tc": 11})
     assert "attention_tc" in str(err.value) and "11" in str(err.value) and "page" in str(err.value)
     assert e._repeat is None and e.ws.zeroed == ["attn_flat_counters"] and e.graph_ws.zeroed == ["attn_flat_counters"]
+
+
+class AheadBackend(FakeBackend):
+    """The same model of a device, with steps that are queued (``launch``) and read later (``result``): the ids of
+    a queued step stay hidden until then, a step may take its tokens from the ids of a queued one, and a slot
+    must not be given back while a queued step that uses it has not been read."""
+
+    def __init__(self, n_slots, vocab=50, ahead=True):
+        super().__init__(n_slots, vocab)
+        self.ahead = ahead
+        self.unread = []            # handles that were launched and not read: each a dict
+        self.launched = 0
+
+    def can_run_ahead(self, params):
+        return self.ahead
+
+    def launch(self, entries, requests, histories, counters, params, feed=None):
+        if feed is not None:
+            src, take = feed
+            assert len(take) == len(entries) and all(list(t) == [0] for _, t in entries), "fed steps bring place holders"
+            entries = [(s, [src["ids"][j]]) for (s, _), j in zip(entries, take)]
+        else:
+            assert all(h["read"] for h in self.unread), "tokens from the host while a step's ids are still unread"
+        ids = []
+        for s, toks in entries:
+            assert s in self.held, "a step uses a slot nobody holds"
+            self.held[s].extend(toks)
+            ids.append(sum(self.held[s]) % self.vocab)
+        self.steps.append([(s, list(t)) for s, t in entries])
+        self.launched += 1
+        h = {"ids": ids, "slots": [s for s, _ in entries], "read": False, "counters": list(counters)}
+        self.unread.append(h)
+        assert sum(1 for x in self.unread if not x["read"]) <= 2, "more than one step ahead"
+        return h
+
+    def result(self, h):
+        assert not h["read"]
+        # steps complete in the order they were queued
+        for x in self.unread:
+            if x is h:
+                break
+            assert x["read"], "a step is read before the one queued before it"
+        h["read"] = True
+        return list(h["ids"])
+
+    def free_slot(self, s):
+        assert all(h["read"] or s not in h["slots"] for h in self.unread), "a slot is given back under a queued step"
+        super().free_slot(s)
+
+
+@pytest.mark.parametrize("max_tokens,stop_tokens,n_slots", [(6, (), 3), (9, (7, 13, 21, 33), 2), (1, (), 4), (12, (0, 1, 2, 3, 4, 5), 3),
+                                                            (5, (), 1)])
+def test_running_one_step_ahead_decides_what_the_plain_loop_decides(max_tokens, stop_tokens, n_slots):
+    prompts = [[1, 2, 3], [4], [5, 6], [7, 8, 9, 10], [11], [3, 3, 3, 3, 3, 3, 3]]
+    opts = GenerationOptions(max_tokens=max_tokens, ignore_eos=True, stop_tokens=stop_tokens, sampler=SamplerParams(greedy=True))
+    plain = FakeBackend(n_slots)
+    want, want_stats = run_generation(plain, prompts, opts, (), n_slots, 4096, 512, 64)
+    ahead = AheadBackend(n_slots)
+    got, stats = run_generation(ahead, prompts, opts, (), n_slots, 4096, 512, 64)
+    assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want]
+    assert (stats.prompt_tokens, stats.completion_tokens) == (want_stats.prompt_tokens, want_stats.completion_tokens)
+    assert not ahead.held and sorted(ahead.free) == list(range(n_slots)) and all(h["read"] for h in ahead.unread)
+    # a sequence that ends by its token limit is never part of a step ahead: without stop tokens no step is wasted
+    if not stop_tokens:
+        assert ahead.launched == len(plain.steps)
+    else:
+        assert len(plain.steps) <= ahead.launched <= len(plain.steps) + len(prompts)
+    # a backend that says it cannot run ahead (penalties need the ids on the host) takes the plain loop
+    sync = AheadBackend(n_slots, ahead=False)
+    again, _ = run_generation(sync, prompts, opts, (), n_slots, 4096, 512, 64)
+    assert sync.launched == 0 and [(r.tokens, r.finish_reason) for r in again] == [(r.tokens, r.finish_reason) for r in want]
+
+
+def test_running_ahead_with_a_callback_that_ends_requests_and_at_the_context_limit():
+    prompts = [[1, 2, 3, 4, 5], [9, 9], [2]]
+    seen = []
+
+    def cb(request, token):
+        seen.append((request, token))
+        return not (request == 1 and len([1 for r, _ in seen if r == 1]) == 3)
+
+    opts = GenerationOptions(max_tokens=50, ignore_eos=True, sampler=SamplerParams(greedy=True))
+    want, _ = run_generation(FakeBackend(3), prompts, opts, (), 3, 4096, 9, 64, cb)
+    plain_seen, seen[:] = list(seen), []
+    ahead = AheadBackend(3)
+    got, _ = run_generation(ahead, prompts, opts, (), 3, 4096, 9, 64, cb)
+    assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want]
+    assert seen == plain_seen
+    assert {r.finish_reason for r in got} == {"context", "stop"}
+    assert max(len(h) for h in ahead.held.values()) if ahead.held else True
+
+
+def test_running_ahead_gives_slots_back_when_a_step_fails():
+    class Failing(AheadBackend):
+        def result(self, h):
+            if self.launched >= 4:
+                raise RuntimeError("a bounded wait ran out")
+            return super().result(h)
+
+        def free_slot(self, s):              # the device is in an unknown state: no ordering to insist on
+            FakeBackend.free_slot(self, s)
+
+    b = Failing(2)
+    opts = GenerationOptions(max_tokens=20, ignore_eos=True, sampler=SamplerParams(greedy=True))
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        run_generation(b, [[1, 2], [3]], opts, (), 2, 4096, 512, 64)
+    assert not b.held and sorted(b.free) == [0, 1]

@@ -104,6 +104,41 @@ def test_a_wait_that_ran_out_ends_generation_with_a_named_error_and_the_engine_r
     assert [r.tokens for r in after] == [r.tokens for r in before]
 
 
+@pytest.mark.parametrize("dn", ["float32", "bfloat16"])
+def test_running_one_step_ahead_generates_what_the_step_by_step_loop_generates(models, dn, monkeypatch):
+    """Generation queues the next step, fed on the device with the ids just sampled, before it reads those ids.
+    With the same seed it must give, token for token, what the loop gives that reads every step's ids before it
+    launches the next: greedy and sampled (no penalties, which need the ids on the host), with stop tokens that
+    end some requests early, more requests than slots, and a request that reaches the end of the context."""
+    from ziglm_b200 import Engine, EngineOptions, GenerationOptions, SamplerParams
+    from ziglm_b200.sampling.device import DeviceSampler
+    folder = models[("B", dn)]
+    V = helpers.CONFIGS["B"]["vocab_size"]
+    eng = Engine.load(folder, EngineOptions(dtype=dn, max_tokens=1024, max_batch=3, max_seq_len=48))
+    prompts = [helpers.random_tokens(n, V, 500 + n) for n in (5, 17, 2, 40, 9, 1, 30)]
+    launched = []
+    real_launch = DeviceSampler.launch
+    monkeypatch.setattr(DeviceSampler, "launch", lambda self, *a, **k: (launched.append(k.get("feed") is not None),
+                                                                       real_launch(self, *a, **k))[1])
+    for sampler in (SamplerParams(greedy=True), SamplerParams(temperature=0.9, top_k=50, top_p=0.95, min_p=0.0, seed=11,
+                                                              repetition_penalty=1.0)):
+        opts = GenerationOptions(max_tokens=14, sampler=sampler, stop_tokens=[3, 50, 77, 120, 200, 300])
+        del launched[:]
+        ahead, _ = eng.generate(prompts, opts)
+        assert any(launched) and not all(launched)              # steps fed from the device, and the prompts' steps
+        monkeypatch.setattr(DeviceSampler, "can_run_ahead", staticmethod(lambda params: False))
+        del launched[:]
+        plain, _ = eng.generate(prompts, opts)
+        assert not launched
+        monkeypatch.undo()
+        monkeypatch.setattr(DeviceSampler, "launch", lambda self, *a, **k: (launched.append(k.get("feed") is not None),
+                                                                           real_launch(self, *a, **k))[1])
+        assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain]
+        assert "length" in {r.finish_reason for r in ahead} and len({r.finish_reason for r in ahead}) >= 2
+    eng.cache.slots.check()
+    assert eng.cache.slots.slots.n_held == 0
+
+
 def test_stop_tokens_and_model_eos(models):
     from ziglm_b200 import Engine, EngineOptions, GenerationOptions, SamplerParams
     folder = models[("B", "float32")]

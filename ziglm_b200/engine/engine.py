@@ -157,20 +157,32 @@ class Engine:
 
     # -------------------------------------------------------------------- step
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+             want: Optional[Sequence[Sequence[int]]] = None,
+             device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one step.
 
         entries  (slot, tokens) per sequence: the next tokens of that sequence, at least one.
         want     per sequence, the places among its tokens whose logits are wanted
                  (default: the last token of each).
+        device_tokens  int32 on the device, one id per sequence in the order of the entries: the tokens of a
+                 step of one token each, when the host does not know them yet (ids that a sampling kernel
+                 earlier in the stream has written, or will have by the time this step's kernels run).  The ids in
+                 ``entries`` are then place holders (give 0).  The generation loop uses this to launch a step
+                 before it has read the ids of the step before.
         Returns float32 logits [n_wanted, vocab] on the device, in the order of the entries
         and of ``want``, or None if nothing is wanted.  The tensor is scratch of the engine:
         it is overwritten by the next step.
         """
         if not entries:
             raise StepError("a step needs at least one sequence")
+        if device_tokens is not None:
+            if any(len(t) != 1 for _, t in entries):
+                raise StepError("tokens from the device are for steps of one token per sequence")
+            if (not device_tokens.is_cuda or device_tokens.dtype != torch.int32 or device_tokens.dim() != 1
+                    or device_tokens.numel() < len(entries)):
+                raise StepError("device_tokens must be int32 on the device, one id per sequence")
         if want is None and self._repeat is not None:
-            logits = self._repeat_decode(entries)
+            logits = self._repeat_decode(entries, device_tokens)
             if logits is not None:
                 return logits
         self._repeat = None
@@ -207,7 +219,7 @@ class Engine:
         single = all(len(t) == 1 for t in new_tokens)
         max_total = max(p + len(t) for p, t in zip(past, new_tokens))
         if single and want_rows == list(range(B)) and self.options.use_graphs:
-            logits = self._graph_step(slots, past, new_tokens, want_rows)
+            logits = self._graph_step(slots, past, new_tokens, want_rows, device_tokens)
             self.cache.slots.advance(growth)
             self._arm_repeat(slots, want is None or all(list(w) == [0] for w in want))
             return logits
@@ -219,6 +231,7 @@ class Engine:
         host, dev = self._buffers(layout.total)
         pack_batch(layout, host, slots, past, new_tokens, want_rows, tables)
         dev[:layout.total].copy_(host[:layout.total], non_blocking=True)
+        self._feed_tokens(dev, layout, device_tokens)
         self._host_events[self._flip].record()
         self.last_step_h2d_bytes = layout.total * 4
         step = self._context(layout, dev, single, max(len(t) for t in new_tokens), max_total, self.ws, past,
@@ -241,8 +254,15 @@ class Engine:
         return step
 
     # ------------------------------------------------------- decode steps as CUDA graphs
+    @staticmethod
+    def _feed_tokens(dev: torch.Tensor, layout: BatchLayout, device_tokens: Optional[torch.Tensor]) -> None:
+        """Overwrite the token ids of a packed step on the device with ids that are already there."""
+        if device_tokens is not None:
+            at = layout.offsets["tokens"]
+            dev[at:at + layout.n_tokens].copy_(device_tokens[:layout.n_tokens], non_blocking=True)
+
     def _graph_step(self, slots: List[int], past: List[int], new_tokens: List[List[int]],
-                    want_rows: List[int]) -> torch.Tensor:
+                    want_rows: List[int], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """A step in which every sequence brings one token and every logit row is wanted: the launches of
         such a step depend on the batch size alone (everything else is read from device memory), so they are
         captured once per batch size and replayed (the reference does this for its one sequence,
@@ -257,6 +277,7 @@ class Engine:
         host = g.staging()
         pack_batch(g.layout, host, slots, past, new_tokens, want_rows, tables)
         g.dev.copy_(host, non_blocking=True)
+        self._feed_tokens(g.dev, g.layout, device_tokens)
         g.mark_copied()
         self.last_step_h2d_bytes = g.layout.total * 4
         return g.run(past, slots)
@@ -277,7 +298,7 @@ class Engine:
         g = self._graphs[len(slots)]
         self._repeat = _RepeatedDecode(list(slots), g, g.host[g.flip].numpy().copy(), left, lengths)
 
-    def _repeat_decode(self, entries) -> Optional[torch.Tensor]:
+    def _repeat_decode(self, entries, device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         r = self._repeat
         if len(entries) != len(r.slots) or r.left <= 0:
             return None
@@ -305,6 +326,7 @@ class Engine:
         host = g.staging()
         host.numpy()[:] = image
         g.dev.copy_(host, non_blocking=True)
+        self._feed_tokens(g.dev, g.layout, device_tokens)
         g.mark_copied()
         self.last_step_h2d_bytes = g.layout.total * 4
         g.graph.replay()

@@ -14,6 +14,15 @@ of a *backend* (``alloc_slot``, ``free_slot``, ``step_and_sample`` and, if it ha
 one, ``check``, which is called when a batch ends and raises if the device
 reported a fault), so the decisions are tested without a GPU.  If a step raises,
 the slots of the live sequences are given back before the error goes on.
+
+A backend that also has ``launch`` and ``result`` (and says ``can_run_ahead`` for
+the sampling options) lets the loop run one step ahead: it queues the next step,
+whose tokens the device takes from the ids it has just sampled, before it reads
+those ids itself, so the host's work on a step hides behind the step before.  The
+decisions are the same; a sequence that turns out to have ended is then part of
+one more step whose result for it is dropped, and gives its slot back only when
+that step is over.  Sequences that are sure to end with the running step (their
+token limit or the context's end) are left out of the step ahead.
 """
 from __future__ import annotations
 
@@ -115,8 +124,13 @@ def run_generation(backend, prompts: Sequence[Sequence[int]], options: Generatio
         batch = plan_batch(pending, prompt_lens, options.max_tokens, max_batch, max_tokens, max_seq_len, page)
         pending = pending[len(batch):]
         live = [_Live(r, backend.alloc_slot(), 0, [], list(prompts[r])) for r in batch]
+        ahead = (hasattr(backend, "launch") and hasattr(backend, "result")
+                 and getattr(backend, "can_run_ahead", lambda p: False)(options.sampler))
         try:
-            _run_batch(backend, live, True, prompts, options, stop, stats, finish, max_seq_len, callback)
+            if ahead:
+                _run_batch_ahead(backend, live, prompts, options, stop, stats, finish, max_seq_len, callback)
+            else:
+                _run_batch(backend, live, True, prompts, options, stop, stats, finish, max_seq_len, callback)
         except BaseException:
             for s in live:
                 if results[s.request] is None:
@@ -169,6 +183,86 @@ def _run_batch(backend, live: List[_Live], first: bool, prompts, options: Genera
                 s.next_token = tok
                 still.append(s)
         live[:] = still
+        first = False
+    check = getattr(backend, "check", None)
+    if check is not None:
+        check()
+
+
+def _run_batch_ahead(backend, live: List[_Live], prompts, options: GenerationOptions, stop, stats: GenerationStats,
+                     finish, max_seq_len: int, callback) -> None:
+    """One batch, one step ahead of the ids it reads (see the module's text).  ``live`` is kept as the set of
+    sequences that have not given their slot back."""
+    params = options.sampler
+    rows = list(live)                                    # the sequences of the step in flight, in row order
+    for s in rows:
+        s.length = len(prompts[s.request])
+    flying = backend.launch([(s.slot, list(prompts[s.request])) for s in rows], [s.request for s in rows],
+                            [s.history for s in rows], [0] * len(rows), params)
+    lens = [s.length for s in rows]                      # what each slot holds once the step in flight is over
+    ended_early = set()                                  # ended while a step that includes them was already queued
+    waiting = []                                         # (sequence, reason): to be finished when that step is over
+    t_last = time.perf_counter()
+    first = True
+    while flying is not None:
+        # 1. the step after: every sequence that is not known, or sure, to end with the step in flight
+        nxt_rows, take = [], []
+        for j, s in enumerate(rows):
+            if id(s) in ended_early:
+                continue
+            if len(s.out) + 1 >= options.max_tokens or lens[j] >= max_seq_len:
+                continue                                 # its token limit, or the context's end: sure to end
+            nxt_rows.append(s)
+            take.append(j)
+        nxt = None
+        if nxt_rows:
+            nxt = backend.launch([(s.slot, [0]) for s in nxt_rows], [s.request for s in nxt_rows],
+                                 [s.history for s in nxt_rows], [len(s.out) + 1 for s in nxt_rows], params,
+                                 feed=(flying, take))
+            for s in nxt_rows:
+                s.length += 1
+        in_next = set(id(s) for s in nxt_rows)
+        # 2. the ids of the step in flight; what waited for its end can go now
+        sampled = backend.result(flying)
+        now = time.perf_counter()
+        if first:
+            stats.prefill_time_ms += (now - t_last) * 1000.0
+            stats.prompt_tokens += sum(len(prompts[s.request]) for s in rows)
+        else:
+            stats.generation_time_ms += (now - t_last) * 1000.0
+        t_last = now
+        for s, reason in waiting:
+            finish(s, reason)
+            live.remove(s)
+        waiting = []
+        # 3. the same decisions as without running ahead, in row order
+        for j, (s, tok) in enumerate(zip(rows, sampled)):
+            if id(s) in ended_early:
+                continue                                 # this row was queued before its end was known
+            tok = int(tok)
+            reason = None
+            if tok in stop:
+                reason = "stop"                          # the stop token is not emitted
+            else:
+                s.out.append(tok)
+                s.history.append(tok)
+                stats.completion_tokens += 1
+                if callback is not None and callback(s.request, tok) is False:
+                    reason = "stop"
+                elif len(s.out) >= options.max_tokens:
+                    reason = "length"
+                elif lens[j] >= max_seq_len:
+                    reason = "context"
+            if reason is None:
+                continue
+            if id(s) in in_next:
+                ended_early.add(id(s))                   # its slot is in use by the queued step
+                waiting.append((s, reason))
+            else:
+                finish(s, reason)
+                live.remove(s)
+        rows, flying = nxt_rows, nxt
+        lens = [s.length for s in rows]
         first = False
     check = getattr(backend, "check", None)
     if check is not None:
