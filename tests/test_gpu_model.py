@@ -368,9 +368,11 @@ def test_tensor_core_head_sizes_take_the_tensor_core_attention(zoo, name, monkey
         eng.options.use_graphs = True
     eng.free_slot(slot)
     layers = helpers.CONFIGS[name]["num_hidden_layers"]
-    # per layer: norm, q|k|v, attention, o, norm, gate|up with activation, down; then embedding, norm, head.
-    # A norm whose neighbours carry it (a product wide enough to be split over a cluster before it) is no launch.
-    assert 5 * layers + 3 <= kernels.launches() - before <= 7 * layers + 3
+    # Once a step: embedding, the first norm, the last norm, the head.  Per layer: q|k|v, attention (with rotation and
+    # cache write), o, gate|up with activation, down, and one norm kernel: at these narrow widths the o product is
+    # too short to be split over a cluster, so the norm after it is a launch of its own, while the norm after
+    # `down` rides on the products around it.  (At real widths both ride: tests/test_gpu_wide.py counts 5 a layer.)
+    assert kernels.launches() - before == 6 * layers + 4
     assert kernels.attention_tc_status() == 0 and kernels.attention_fmha_status() == 0
 
 
