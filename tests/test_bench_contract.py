@@ -28,19 +28,43 @@ def test_reference_arm_prints_its_unavailable_line():
 
 
 def test_byte_and_flop_counts():
+    """The roofline's bytes and FLOPs, checked against sources that are not bench.py's formulas: the tensors
+    the model declares (what a decode step has to read), the figures the published shapes are known by, and a
+    count made tensor by tensor."""
     sys.path.insert(0, ROOT)
     import bench
+    from ziglm_b200 import config_from_dict
+    from ziglm_b200.engine.model import declare_parameters
+    for name, cfg, batch, context in (("8b", bench.LLAMA_8B, 8, 4096), ("1b", bench.LLAMA_1B, 64, 600),
+                                      ("13b", bench.LLAMA_13B, 8, 2304)):
+        conf = config_from_dict(cfg)
+        declared = declare_parameters(conf.model_spec())
+        elements = {n: 1 for n in declared}
+        for n, decl in declared.items():
+            for k in decl.shape:
+                elements[n] *= k
+        # every declared tensor is read once, except the embedding table of a model with a head of its own,
+        # of which the step gathers `batch` rows; the cache: keys and values of every layer for every live token
+        weights = sum(elements.values())
+        if not conf.tie_word_embeddings:
+            weights -= elements["model.embed_tokens.weight"]
+        kv_per_token = 2 * conf.num_hidden_layers * conf.num_key_value_heads * conf.head_dim
+        want = 2 * (weights + kv_per_token * batch * context + batch * conf.hidden_size)
+        got = bench.decode_bytes(cfg, conf.num_hidden_layers, batch, context)
+        assert abs(got - want) <= 1e-9 * want, name
+        assert bench.decode_bytes(cfg, conf.num_hidden_layers, batch, 0, cached_tokens=batch * context) == got
+    # the figures the shapes are known by: 8.03 B parameters (15.01 GB of them read by a step), 128 KiB of cache a token
+    assert abs(bench.decode_bytes(bench.LLAMA_8B, 32, 1, 0) - 15.01e9) < 0.01e9
+    assert bench.decode_bytes(bench.LLAMA_8B, 32, 1, 1) - bench.decode_bytes(bench.LLAMA_8B, 32, 1, 0) == 128 * 1024
+    assert abs(bench.decode_bytes(bench.LLAMA_8B, 32, 8, 4096) - 19.30e9) < 0.01e9
+    # the prompt, product by product: 2 FLOPs per weight element and token, the causal half of attention
+    # (scores and weighted values, 2 FLOPs each per query, key and head dimension), the head for one row
     cfg = bench.LLAMA_8B
-    d, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
-    q = cfg["num_attention_heads"] * cfg["head_dim"]
-    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
-    per_layer = d * q + 2 * d * kv + q * d + 3 * d * i
-    # a decode step reads every weight it uses once (the embedding rows it gathers are not counted) and the
-    # keys and values of the live requests
-    want = 2 * (32 * per_layer + d * v) + 8 * 4096 * 32 * 2 * kv * 2
-    got = bench.decode_bytes(cfg, 32, 8, 4096)
-    assert abs(got - want) <= 0.01 * want
-    # the prompt: products of every token, the causal half of attention, the head for one row
-    flops = bench.prefill_flops(cfg, 32, 2048)
-    want_f = 32 * (2 * 2048 * per_layer + 2 * 2 * q * 2048 * 2049 / 2) + 2 * d * v
-    assert abs(flops - want_f) <= 1e-6 * want_f
+    T, flops = 2048, 0
+    for n, decl in declare_parameters(config_from_dict(cfg).model_spec()).items():
+        if len(decl.shape) == 2 and "layers." in n:
+            flops += 2 * T * decl.shape[0] * decl.shape[1]
+    flops += 32 * 2 * 2 * (32 * 128) * sum(p + 1 for p in range(T))
+    flops += 2 * 4096 * 128256
+    assert abs(bench.prefill_flops(cfg, 32, T) - flops) <= 1e-9 * flops
+    assert abs(flops - 29.69e12) < 0.01e12
