@@ -98,7 +98,7 @@ def test_more_requests_than_slots_run_batch_after_batch_and_slots_are_used_again
         assert r.tokens == expected(p, 3)[0]
 
 
-def test_cache_budget_limits_a_batch():
+def test_cache_room_limits_a_batch():
     lens = [100, 100, 100, 100]
     assert plan_batch([0, 1, 2, 3], lens, 28, 8, 256, 512, 64) == [0, 1]        # 128 + 128 positions
     assert plan_batch([2, 3], lens, 28, 8, 256, 512, 64) == [2, 3]
