@@ -116,10 +116,11 @@ def test_gemm_generic(K, xd, wd, yd, M, N, K_):
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 8, 9, 16, 17, 32])
-@pytest.mark.parametrize("N,K_", [(130, 64), (33, 1000), (4100, 520), (31, 4), (256, 4096)])
+@pytest.mark.parametrize("N,K_", [(130, 64), (33, 1000), (4100, 520), (31, 4), (256, 4096), (16500, 200), (20001, 36)])
 def test_few_tokens_in_float32_take_the_streaming_kernel_and_keep_the_order_of_the_sums(K, M, N, K_):
     """Float operands with at most 32 tokens run a kernel of their own (32 weight rows a block, a thread per
-    row and token).  It adds every output's products in ascending k like the tiled kernel, so the rows of a
+    row and token; 128 rows a block, every warp with rows of its own, from 16,384 rows on with at most 8
+    tokens).  It adds every output's products in ascending k like the tiled kernel, so the rows of a
     step of few tokens equal, bit for bit, the same rows computed inside a step of many tokens."""
     x, w, b = rnd((M, K_), torch.float32, seed=5), rnd((N, K_), torch.float32, seed=6), rnd((N,), torch.float32, seed=7)
     out = torch.full((M, N), 9.0, device=DEV)

@@ -14,8 +14,8 @@
 // Two kernels keep that rule.  gemm_generic_kernel tiles 64 tokens x 64 weight
 // rows; a step of a few tokens would use a sixty-fourth of such a tile and too few
 // blocks to draw on the memory system, so float operands with at most 32 tokens go
-// to gemm_skinny_kernel, which streams 32 weight rows a block through a ring of
-// asynchronous copies and gives every (row, token) pair to one thread.
+// to gemm_skinny_kernel, which streams 32 or 128 weight rows a block through a ring
+// of asynchronous copies and gives every (row, token) pair to one thread.
 #include "common.cuh"
 
 namespace zlm {
@@ -91,12 +91,19 @@ gemm_generic_kernel(const TX* __restrict__ X, const TW* __restrict__ W, const TB
 }
 
 // ------------------------------------------------------ few tokens, float operands
-// A block owns SK_ROWS weight rows and all M <= 4 * TT tokens.  Lane l of every warp owns row l; warp w owns the
-// tokens w * TT .. w * TT + TT - 1, so a thread carries TT running sums.  The K range comes in chunks of SK_BK
-// floats: all threads issue 16-byte asynchronous copies of the rows' chunk and of the tokens' chunk into one
-// of SK_STAGES stages, and compute from the oldest stage while the younger ones are in flight.  A row of a
-// stage is padded by four floats, so that the 32 lanes' 16-byte reads of their rows fall in different banks.
-constexpr int SK_ROWS = 32, SK_WARPS = 4, SK_BK = 128, SK_STAGES = 4, SK_LD = SK_BK + 4;
+// A block of four warps owns 32 * RW weight rows and all M <= (4 / RW) * TT tokens.  Warp w owns the rows of row
+// group w % RW (lane l: row l of the group) and the tokens of token group w / RW (TT of them), so a thread carries
+// TT running sums.  The K range comes in chunks of SK_BK / RW floats: all threads issue 16-byte asynchronous
+// copies of the rows' chunk and of the tokens' chunk into one of SK_STAGES stages, and compute from the oldest
+// stage while the younger ones are in flight.  A row of a stage is padded by four floats, so that the 32 lanes'
+// 16-byte reads of their rows fall in different banks.
+//
+// RW = 1 (32 rows a block, up to 32 tokens over the four warps) gives narrow products enough blocks to fill the
+// device.  RW = 4 (128 rows a block, up to 8 tokens, every warp with rows of its own) is for wide products with
+// few tokens: a weight value is then read from shared memory by one warp instead of four, and it is shared memory
+// reads that bound these kernels.
+constexpr int SK_WARPS = 4, SK_BK = 128, SK_STAGES = 4;
+template <int RW> struct SkChunk { static constexpr int value = SK_BK / RW; };   // floats of K a stage
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, int src_bytes) {
     // copies src_bytes (0..16) and fills the rest of the 16 bytes with zeros
@@ -108,35 +115,47 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int TT, typename TB, bool ACC>
+template <int RW, int TT, typename TB, bool ACC>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const float* __restrict__ X, const float* __restrict__ W, const TB* __restrict__ bias,
                    float* __restrict__ Y, int M, int N, int K, long ldx, long ldw, long ldy) {
-    constexpr int TOK = SK_WARPS * TT;                       // token rows staged
+    constexpr int ROWS = 32 * RW;                            // weight rows staged
+    constexpr int TOK = (SK_WARPS / RW) * TT;                // token rows staged
+    constexpr int BKC = SkChunk<RW>::value, LD = BKC + 4;          // floats of K a stage, and a staged row's pitch
     extern __shared__ __align__(16) float sk_smem[];
-    float* Ws = sk_smem;                                     // [SK_STAGES][SK_ROWS][SK_LD]
-    float* Xs = sk_smem + SK_STAGES * SK_ROWS * SK_LD;       // [SK_STAGES][TOK][SK_LD]
+    float* Ws = sk_smem;                                     // [SK_STAGES][ROWS][LD]
+    float* Xs = sk_smem + SK_STAGES * ROWS * LD;             // [SK_STAGES][TOK][LD]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n0 = blockIdx.x * SK_ROWS;
-    const int n_chunks = (K + SK_BK - 1) / SK_BK;
+    const int row_group = warp % RW, token_group = warp / RW;
+    const int n0 = blockIdx.x * ROWS;
+    const int n_chunks = (K + BKC - 1) / BKC;
+
+    // The pieces of 16 bytes a thread copies are the same in every chunk: piece j of this thread is row
+    // tid / PPR + j * RSTEP at float (tid % PPR) * 4 of the chunk.  Row offsets are kept, not recomputed.
+    constexpr int PPR = BKC / 4;                             // pieces a row
+    constexpr int RSTEP = SK_WARPS * 32 / PPR;               // rows between a thread's pieces
+    constexpr int WP = ROWS / RSTEP, XP = (TOK + RSTEP - 1) / RSTEP;
+    const int pr = tid / PPR, pc = (tid % PPR) * 4;
+    const float* wsrc[WP];
+#pragma unroll
+    for (int j = 0; j < WP; ++j)                             // rows beyond N repeat the last one and are not stored
+        wsrc[j] = W + (long)min(n0 + pr + j * RSTEP, N - 1) * ldw + pc;
+    const float* xsrc[XP];
+#pragma unroll
+    for (int j = 0; j < XP; ++j) xsrc[j] = X + (long)min(pr + j * RSTEP, M - 1) * ldx + pc;
 
     auto issue = [&](int chunk) {
-        const int stage = chunk % SK_STAGES, k0 = chunk * SK_BK;
-        float* ws = Ws + stage * SK_ROWS * SK_LD;
-        float* xs = Xs + stage * TOK * SK_LD;
-        // a row's chunk is SK_BK / 4 pieces of 16 bytes; pieces beyond K are zeros
-        for (int i = tid; i < SK_ROWS * (SK_BK / 4); i += SK_WARPS * 32) {
-            const int r = i / (SK_BK / 4), c = (i % (SK_BK / 4)) * 4;
-            const int gr = min(n0 + r, N - 1);               // rows beyond N repeat the last one and are not stored
-            const int left = (K - (k0 + c)) * 4;
-            cp_async_16(ws + r * SK_LD + c, W + (long)gr * ldw + k0 + (left > 0 ? c : 0), left >= 16 ? 16 : (left > 0 ? left : 0));
-        }
-        for (int i = tid; i < TOK * (SK_BK / 4); i += SK_WARPS * 32) {
-            const int r = i / (SK_BK / 4), c = (i % (SK_BK / 4)) * 4;
-            const int gr = min(r, M - 1);
-            const int left = (K - (k0 + c)) * 4;
-            cp_async_16(xs + r * SK_LD + c, X + (long)gr * ldx + k0 + (left > 0 ? c : 0), left >= 16 ? 16 : (left > 0 ? left : 0));
-        }
+        const int stage = chunk % SK_STAGES, k0 = chunk * BKC;
+        float* ws = Ws + stage * ROWS * LD + pr * LD + pc;
+        float* xs = Xs + stage * TOK * LD + pr * LD + pc;
+        // pieces beyond K are zeros (K is a multiple of 4: a piece is whole or absent)
+        const bool have = k0 + pc < K;
+        const int bytes = have ? 16 : 0, at = have ? k0 : 0;
+#pragma unroll
+        for (int j = 0; j < WP; ++j) cp_async_16(ws + j * RSTEP * LD, wsrc[j] + at, bytes);
+#pragma unroll
+        for (int j = 0; j < XP; ++j)
+            if (pr + j * RSTEP < TOK) cp_async_16(xs + j * RSTEP * LD, xsrc[j] + at, bytes);
     };
 
     for (int c = 0; c < SK_STAGES - 1; ++c) {
@@ -146,7 +165,7 @@ gemm_skinny_kernel(const float* __restrict__ X, const float* __restrict__ W, con
     float acc[TT];
 #pragma unroll
     for (int t = 0; t < TT; ++t) acc[t] = 0.f;
-    const bool active = warp * TT < M;                       // warps whose tokens do not exist only help copying
+    const bool active = token_group * TT < M;                // warps whose tokens do not exist only help copying
 
     for (int chunk = 0; chunk < n_chunks; ++chunk) {
         cp_async_wait<SK_STAGES - 2>();                      // this thread's copies of the oldest stage have landed
@@ -154,29 +173,44 @@ gemm_skinny_kernel(const float* __restrict__ X, const float* __restrict__ W, con
         if (chunk + SK_STAGES - 1 < n_chunks) issue(chunk + SK_STAGES - 1);
         cp_async_commit();
         if (active) {
-            const float* ws = Ws + (chunk % SK_STAGES) * SK_ROWS * SK_LD + lane * SK_LD;
-            const float* xs = Xs + (chunk % SK_STAGES) * TOK * SK_LD + warp * TT * SK_LD;
-#pragma unroll 4
-            for (int k = 0; k < SK_BK; k += 4) {
-                const float4 w = *reinterpret_cast<const float4*>(ws + k);
+            const float* ws = Ws + (chunk % SK_STAGES) * ROWS * LD + (row_group * 32 + lane) * LD;
+            const float* xs = Xs + (chunk % SK_STAGES) * TOK * LD + token_group * TT * LD;
+            // the loads of the next four k are issued before the sums of these four: with eight warps an SM
+            // nothing else hides the latency of shared memory
+            float4 w = *reinterpret_cast<const float4*>(ws);
+            float4 x[TT];
+#pragma unroll
+            for (int t = 0; t < TT; ++t) x[t] = *reinterpret_cast<const float4*>(xs + t * LD);
+#pragma unroll
+            for (int k = 0; k < BKC; k += 4) {
+                float4 wn = w, xn[TT];
+#pragma unroll
+                for (int t = 0; t < TT; ++t) xn[t] = x[t];
+                if (k + 4 < BKC) {
+                    wn = *reinterpret_cast<const float4*>(ws + k + 4);
+#pragma unroll
+                    for (int t = 0; t < TT; ++t) xn[t] = *reinterpret_cast<const float4*>(xs + t * LD + k + 4);
+                }
 #pragma unroll
                 for (int t = 0; t < TT; ++t) {
-                    const float4 x = *reinterpret_cast<const float4*>(xs + t * SK_LD + k);
                     // ascending k, one fused multiply-add each: the order of gemm_generic_kernel
-                    acc[t] = fmaf(x.x, w.x, acc[t]);
-                    acc[t] = fmaf(x.y, w.y, acc[t]);
-                    acc[t] = fmaf(x.z, w.z, acc[t]);
-                    acc[t] = fmaf(x.w, w.w, acc[t]);
+                    acc[t] = fmaf(x[t].x, w.x, acc[t]);
+                    acc[t] = fmaf(x[t].y, w.y, acc[t]);
+                    acc[t] = fmaf(x[t].z, w.z, acc[t]);
+                    acc[t] = fmaf(x[t].w, w.w, acc[t]);
                 }
+                w = wn;
+#pragma unroll
+                for (int t = 0; t < TT; ++t) x[t] = xn[t];
             }
         }
     }
-    const int gn = n0 + lane;
+    const int gn = n0 + row_group * 32 + lane;
     if (!active || gn >= N) return;
     const float b = bias ? to_float(bias[gn]) : 0.f;
 #pragma unroll
     for (int t = 0; t < TT; ++t) {
-        const int gm = warp * TT + t;
+        const int gm = token_group * TT + t;
         if (gm >= M) break;
         float v = acc[t];
         if (bias) v += b;
@@ -186,28 +220,33 @@ gemm_skinny_kernel(const float* __restrict__ X, const float* __restrict__ W, con
     }
 }
 
-template <int TT, typename TB, bool ACC>
+template <int RW, int TT, typename TB, bool ACC>
 static int launch_skinny_one(const float* X, const float* W, const void* bias, float* Y, int M, int N, int K, long ldx,
                              long ldw, long ldy, cudaStream_t stream) {
-    const int smem = SK_STAGES * (SK_ROWS + SK_WARPS * TT) * SK_LD * (int)sizeof(float);
+    constexpr int ROWS = 32 * RW, TOK = (SK_WARPS / RW) * TT, LD = SkChunk<RW>::value + 4;
+    const int smem = SK_STAGES * (ROWS + TOK) * LD * (int)sizeof(float);
     static bool configured = false;                          // one flag per kernel: this function is its only launcher
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<TT, TB, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<RW, TT, TB, ACC>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_skinny_kernel<TT, TB, ACC><<<(N + SK_ROWS - 1) / SK_ROWS, SK_WARPS * 32, smem, stream>>>(
+    gemm_skinny_kernel<RW, TT, TB, ACC><<<(N + ROWS - 1) / ROWS, SK_WARPS * 32, smem, stream>>>(
         X, W, (const TB*)bias, Y, M, N, K, ldx, ldw, ldy);
     return launch_status();
 }
 
-template <int TT, typename TB>
+template <int RW, int TT, typename TB>
 static int launch_skinny_tt(const float* X, const float* W, const void* bias, float* Y, int accumulate, int M, int N,
                             int K, long ldx, long ldw, long ldy, cudaStream_t stream) {
-    if (accumulate) return launch_skinny_one<TT, TB, true>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, stream);
-    return launch_skinny_one<TT, TB, false>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, stream);
+    if (accumulate) return launch_skinny_one<RW, TT, TB, true>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, stream);
+    return launch_skinny_one<RW, TT, TB, false>(X, W, bias, Y, M, N, K, ldx, ldw, ldy, stream);
 }
+
+// Products with at least this many weight rows and at most 8 tokens give every warp rows of its own (RW = 4):
+// there are then still more blocks than the device holds at once.
+constexpr int SK_WIDE_N = 16384;
 
 // Float operands whose rows start on 16-byte boundaries, at most 32 tokens.  Returns ZLM_ERR_UNSUPPORTED otherwise.
 static int launch_skinny(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int accumulate, int M,
@@ -215,18 +254,24 @@ static int launch_skinny(const void* X, const void* W, const void* bias, int bia
     if (M > 8 * SK_WARPS || (K & 3) || (ldx & 3) || (ldw & 3) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
         return ZLM_ERR_UNSUPPORTED;
     if (bias != nullptr && bias_dtype != ZLM_F32 && bias_dtype != ZLM_BF16) return ZLM_ERR_UNSUPPORTED;
-    const int tt = (M + SK_WARPS - 1) / SK_WARPS;            // tokens per warp: 1, 2, 4 or 8
     const float* x = (const float*)X;
     const float* w = (const float*)W;
     float* y = (float*)Y;
-#define ZLM_SKINNY(TTV)                                                                                              \
+#define ZLM_SKINNY(RWV, TTV)                                                                                         \
     (bias != nullptr && bias_dtype == ZLM_BF16                                                                       \
-         ? launch_skinny_tt<TTV, __nv_bfloat16>(x, w, bias, y, accumulate, M, N, K, ldx, ldw, ldy, stream)             \
-         : launch_skinny_tt<TTV, float>(x, w, bias, y, accumulate, M, N, K, ldx, ldw, ldy, stream))
-    if (tt <= 1) return ZLM_SKINNY(1);
-    if (tt <= 2) return ZLM_SKINNY(2);
-    if (tt <= 4) return ZLM_SKINNY(4);
-    return ZLM_SKINNY(8);
+         ? launch_skinny_tt<RWV, TTV, __nv_bfloat16>(x, w, bias, y, accumulate, M, N, K, ldx, ldw, ldy, stream)        \
+         : launch_skinny_tt<RWV, TTV, float>(x, w, bias, y, accumulate, M, N, K, ldx, ldw, ldy, stream))
+    if (N >= SK_WIDE_N && M <= 8) {                          // every warp its own rows, all tokens
+        if (M <= 1) return ZLM_SKINNY(4, 1);
+        if (M <= 2) return ZLM_SKINNY(4, 2);
+        if (M <= 4) return ZLM_SKINNY(4, 4);
+        return ZLM_SKINNY(4, 8);
+    }
+    const int tt = (M + SK_WARPS - 1) / SK_WARPS;            // tokens per warp: 1, 2, 4 or 8
+    if (tt <= 1) return ZLM_SKINNY(1, 1);
+    if (tt <= 2) return ZLM_SKINNY(1, 2);
+    if (tt <= 4) return ZLM_SKINNY(1, 4);
+    return ZLM_SKINNY(1, 8);
 #undef ZLM_SKINNY
 }
 
