@@ -141,6 +141,36 @@ def test_few_tokens_in_float32_take_the_streaming_kernel_and_keep_the_order_of_t
     assert torch.equal(wide_y[:, :N], ref[:M]) and (wide_y[:, N:] == 2.0).all()
 
 
+@pytest.mark.parametrize("M,N,K_", [(97, 130, 64), (200, 257, 1000), (128, 128, 16), (300, 31, 4), (129, 640, 520)])
+def test_many_tokens_in_float32_take_the_large_tiles_and_keep_the_order_of_the_sums(K, M, N, K_):
+    """Float operands with more than 96 tokens run tiles of 128 x 128.  Every output is still one thread's sum in
+    ascending k: rows computed there equal, bit for bit, the same rows computed 70 at a time (the 64 x 64 tiles)
+    and 8 at a time (the streaming kernel); so do rows that accumulate and rows of wider buffers; unaligned rows
+    fall back to the small tiles and give the same bits."""
+    x, w, b = rnd((M, K_), torch.float32, seed=15), rnd((N, K_), torch.float32, seed=16), rnd((N,), torch.float32, seed=17)
+    out = torch.full((M, N), 9.0, device=DEV)
+    K.gemm_generic(x.to(DEV), w.to(DEV), out, bias=b.to(DEV))
+    assert torch.allclose(out.cpu(), P.linear(x, w, b), atol=1e-5 * max(1.0, K_ ** 0.5), rtol=1e-5)
+    for at, n in ((0, 70), (M - 70, 70), (5, 8), (M - 1, 1)):
+        part = torch.empty(n, N, device=DEV)
+        K.gemm_generic(x[at:at + n].to(DEV), w.to(DEV), part, bias=b.to(DEV))
+        assert torch.equal(part, out[at:at + n]), (at, n)
+    base = rnd((M, N + 3), torch.float32, seed=18).to(DEV)
+    acc = base.clone()
+    wide_x = torch.zeros(M, K_ + 8, device=DEV)
+    wide_x[:, 4:4 + K_] = x.to(DEV)
+    K.gemm_generic(wide_x[:, 4:4 + K_], w.to(DEV), acc[:, :N], accumulate=True)
+    plain = torch.empty(M, N, device=DEV)
+    K.gemm_generic(x.to(DEV), w.to(DEV), plain)
+    assert torch.equal(acc[:, :N], base[:, :N] + plain) and torch.equal(acc[:, N:], base[:, N:])
+    # rows that start on no 16-byte boundary: the small tiles, the same bits
+    odd_x = torch.zeros(M, K_ + 8, device=DEV)
+    odd_x[:, 1:1 + K_] = x.to(DEV)
+    other = torch.empty(M, N, device=DEV)
+    K.gemm_generic(odd_x[:, 1:1 + K_], w.to(DEV), other)
+    assert torch.equal(other, plain)
+
+
 def test_gemm_generic_strided_rows_and_true_float32(K):
     """Rows of a wider buffer; and float32 products are not rounded to a shorter mantissa."""
     buf = rnd((10, 100), torch.float32, seed=9).to(DEV)

@@ -11,8 +11,9 @@
 // ascending k with fmaf, so a value does not depend on M, on where the row sits
 // in the batch, or on the tile it falls in.
 //
-// Two kernels keep that rule.  gemm_generic_kernel tiles 64 tokens x 64 weight
-// rows; a step of a few tokens would use a sixty-fourth of such a tile and too few
+// Three kernels keep that rule.  gemm_generic_kernel tiles 64 tokens x 64 weight
+// rows and takes every operand type; float operands with more than 96 tokens go to
+// gemm_large_kernel (128 x 128 tiles, 64 outputs a thread); a step of a few tokens would use a sixty-fourth of such a tile and too few
 // blocks to draw on the memory system, so float operands with at most 32 tokens go
 // to gemm_skinny_kernel, which streams 32 or 128 weight rows a block through a ring
 // of asynchronous copies and gives every (row, token) pair to one thread.
@@ -88,6 +89,130 @@ gemm_generic_kernel(const TX* __restrict__ X, const TW* __restrict__ W, const TB
             else *dst = from_float<TY>(v);
         }
     }
+}
+
+// ------------------------------------------------------ many tokens, float operands
+// Tiles of 128 tokens x 128 weight rows for float operands whose rows start on 16-byte boundaries: 256 threads,
+// 8 x 8 outputs a thread (two groups of four tokens, two groups of four rows, so that a thread reads its 16
+// operands of a k with four 16-byte loads), K in steps of 16 through two buffers of shared memory: the next
+// step's 16-byte global loads are in flight while this step is summed.  Every output is still one thread's sum
+// in ascending k, one fused multiply-add each.
+constexpr int LM = 128, LN = 128, LK = 16, LLD = 128 + 4;
+
+template <typename TB, bool ACC>
+__global__ void __launch_bounds__(256, 2)
+gemm_large_kernel(const float* __restrict__ X, const float* __restrict__ W, const TB* __restrict__ bias,
+                  float* __restrict__ Y, int M, int N, int K, long ldx, long ldw, long ldy) {
+    __shared__ __align__(16) float As[2][LK][LLD];           // [k][token]
+    __shared__ __align__(16) float Bs[2][LK][LLD];           // [k][weight row]
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * LM, n0 = blockIdx.x * LN;
+    // loader: 128 rows x 16 k = 512 pieces of four k; a thread loads rows lr and lr + 64 at k offset lk
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    // rows beyond M or N repeat the last one; their outputs are not stored
+    const float* xsrc[2];
+    const float* wsrc[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        xsrc[h] = X + (long)min(m0 + lr + 64 * h, M - 1) * ldx + lk;
+        wsrc[h] = W + (long)min(n0 + lr + 64 * h, N - 1) * ldw + lk;
+    }
+    float4 xa[2], wb[2];
+    auto fetch = [&](int k0) {                               // K is a multiple of 4: a piece is whole or absent
+        if (k0 + lk < K) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                xa[h] = *reinterpret_cast<const float4*>(xsrc[h] + k0);
+                wb[h] = *reinterpret_cast<const float4*>(wsrc[h] + k0);
+            }
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) xa[h] = wb[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto stage = [&](int buf) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = lr + 64 * h;
+            As[buf][lk + 0][r] = xa[h].x; As[buf][lk + 1][r] = xa[h].y;
+            As[buf][lk + 2][r] = xa[h].z; As[buf][lk + 3][r] = xa[h].w;
+            Bs[buf][lk + 0][r] = wb[h].x; Bs[buf][lk + 1][r] = wb[h].y;
+            Bs[buf][lk + 2][r] = wb[h].z; Bs[buf][lk + 3][r] = wb[h].w;
+        }
+    };
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+    fetch(0);
+    stage(0);
+    __syncthreads();
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += LK) {
+        const bool more = k0 + LK < K;
+        if (more) fetch(k0 + LK);
+#pragma unroll
+        for (int k = 0; k < LK; ++k) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][64 + tx * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (more) {
+            stage(buf ^ 1);                                  // the other buffer was last read one step ago
+            __syncthreads();
+            buf ^= 1;
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+        if (gm >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+            if (gn >= N) continue;
+            float v = acc[i][j];
+            if (bias) v += to_float(bias[gn]);
+            float* dst = Y + (long)gm * ldy + gn;
+            if (ACC) *dst = *dst + v;
+            else *dst = v;
+        }
+    }
+}
+
+// Float operands whose rows start on 16-byte boundaries, more than 96 tokens.  ZLM_ERR_UNSUPPORTED otherwise.
+static int launch_large(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int accumulate, int M,
+                        int N, int K, long ldx, long ldw, long ldy, cudaStream_t stream) {
+    if (M <= 96 || (K & 3) || (ldx & 3) || (ldw & 3) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        return ZLM_ERR_UNSUPPORTED;
+    if (bias != nullptr && bias_dtype != ZLM_F32 && bias_dtype != ZLM_BF16) return ZLM_ERR_UNSUPPORTED;
+    const dim3 grid((N + LN - 1) / LN, (M + LM - 1) / LM);
+    const float* x = (const float*)X;
+    const float* w = (const float*)W;
+    float* y = (float*)Y;
+#define ZLM_LARGE(TBV, ACCV)                                                                                         \
+    gemm_large_kernel<TBV, ACCV><<<grid, 256, 0, stream>>>(x, w, (const TBV*)bias, y, M, N, K, ldx, ldw, ldy)
+    if (bias != nullptr && bias_dtype == ZLM_BF16) {
+        if (accumulate) ZLM_LARGE(__nv_bfloat16, true);
+        else ZLM_LARGE(__nv_bfloat16, false);
+    } else {
+        if (accumulate) ZLM_LARGE(float, true);
+        else ZLM_LARGE(float, false);
+    }
+#undef ZLM_LARGE
+    return launch_status();
 }
 
 // ------------------------------------------------------ few tokens, float operands
@@ -321,6 +446,10 @@ ZLM_EXPORT int zlm_gemm_generic(const void* X, int x_dtype, const void* W, int w
     if (K <= 0 || ldx < K || ldw < K || ldy < N) return ZLM_ERR_BAD_ARG;
     if (x_dtype == ZLM_F32 && w_dtype == ZLM_F32 && y_dtype == ZLM_F32 && M <= 8 * SK_WARPS) {
         const int rc = launch_skinny(X, W, bias, bias_dtype, Y, accumulate, M, N, K, ldx, ldw, ldy, stream);
+        if (rc != ZLM_ERR_UNSUPPORTED) return rc;
+    }
+    if (x_dtype == ZLM_F32 && w_dtype == ZLM_F32 && y_dtype == ZLM_F32) {
+        const int rc = launch_large(X, W, bias, bias_dtype, Y, accumulate, M, N, K, ldx, ldw, ldy, stream);
         if (rc != ZLM_ERR_UNSUPPORTED) return rc;
     }
     if (x_dtype == ZLM_F32 && w_dtype == ZLM_F32)
