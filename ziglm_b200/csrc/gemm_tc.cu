@@ -135,16 +135,23 @@ __device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* t
                                         : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.bias)[f]);
     const int out_f = GLU ? f >> 1 : f;
     const int out_n = GLU ? a.N >> 1 : a.N;
+    // The staging area is sized for float32 sub-tiles of 128 features; a bf16 sub-tile is half of that and a
+    // gated one a quarter, so the same bytes hold two or four times as many sub-tiles on their way out, and a
+    // tile of few sub-tiles never waits for a store to have read its buffer.
+    constexpr int OUT_BYTES = (MODE == OUT_F32 || MODE == OUT_F32_ACC) ? 4 : 2;
+    constexpr int SUB_STRIDE = C::SUB * OUT_COLS * OUT_BYTES;
+    constexpr int NB = BN > C::SUB ? C::STAGING / SUB_STRIDE : C::NBUF;    // a tile of one sub-tile has no use for more
+    static_assert(NB >= C::NBUF && SUB_STRIDE % 128 == 0, "staging buffers");
 #pragma unroll 1
     for (int c = 0; c < BN / 16; ++c) {
         if (tok0 + c * 16 >= a.T) break;            // whole chunk beyond the last token (uniform per block)
         const int sub_row = (c * 16) % C::SUB;       // row of this chunk inside the staged sub-tile
-        const int buf = sub_idx % C::NBUF;
-        float* stage_f = reinterpret_cast<float*>(stage_base + buf * C::SUB_BYTES);
+        const int buf = sub_idx % NB;
+        float* stage_f = reinterpret_cast<float*>(stage_base + buf * SUB_STRIDE);
         __nv_bfloat16* stage_h = reinterpret_cast<__nv_bfloat16*>(stage_f);
-        if (a.tma_store && sub_row == 0 && sub_idx >= C::NBUF) {
+        if (a.tma_store && sub_row == 0 && sub_idx >= NB) {
             // the store that last used this buffer must have read it before it is overwritten
-            if (warp == 2 && lane == 0) tma_store_wait_read_keep<C::NBUF - 1>();
+            if (warp == 2 && lane == 0) tma_store_wait_read_keep<NB - 1>();
             asm volatile("bar.sync 1, 256;" ::: "memory");
         }
         uint32_t v[16];
@@ -189,8 +196,8 @@ __device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* t
             if (warp == 2 && lane == 0) {
                 const int x = GLU ? row0 >> 1 : row0;
                 const int y = tok0 + c * 16 - sub_row;
-                if (MODE == OUT_F32_ACC) tma_reduce_add_2d(tmap_y, stage_out + buf * C::SUB_BYTES, x, y);
-                else tma_store_2d(tmap_y, stage_out + buf * C::SUB_BYTES, x, y);
+                if (MODE == OUT_F32_ACC) tma_reduce_add_2d(tmap_y, stage_out + buf * SUB_STRIDE, x, y);
+                else tma_store_2d(tmap_y, stage_out + buf * SUB_STRIDE, x, y);
                 tma_store_commit();
             }
         }
@@ -224,7 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     float* partial = reinterpret_cast<float*>(smem);   // split-K only (one tile per block): [BN][128] floats
 
     __shared__ float inv_s[64];                     // row scales of a product that completes a norm
-    __shared__ float norm_red[2][4];                // sums of squares of the four warps of an epilogue half
+    __shared__ float norm_red[2][4][4];             // sums of squares: [epilogue half][token of a group][warp]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = a.splits > 1 ? cluster_rank() : 0u;
     const int kb0 = (int)rank * a.kb_per_split;
@@ -396,52 +403,131 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             uint32_t remote[8];
 #pragma unroll
             for (int r = 0; r < 8; ++r) remote[r] = r < a.splits ? map_to_rank(part_addr, (uint32_t)r) : 0u;
-            for (int cc = c_lo + egroup; cc < c_hi && good; cc += 2) {
-                const int tok = tok0 + cc;
-                if (tok >= a.T) break;
-                float part[8];
-#pragma unroll
-                for (int r = 0; r < 8; ++r)
-                    part[r] = r < a.splits ? ld_cluster_f32(remote[r] + 4u * (cc * TC_BM + f_local)) : 0.f;
-                float val = part[0];
-#pragma unroll
-                for (int r = 1; r < 8; ++r) val += part[r];
-                if (a.scale_ssq != nullptr) val *= inv_s[cc];
-                val += bias_v;
-                if (GLU) {
-                    const float up = __shfl_down_sync(0xffffffffu, val, 1);
-                    const float g = val;
-                    val = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
-                }
-                if (writer && out_f < out_n) {
-                    if (MODE == OUT_BF16 || GLU)
-                        reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
-                    else if (MODE == OUT_F32_ACC && a.norm_gain == nullptr)   // one adder per element: the order is fixed
-                        atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
-                    else if (MODE != OUT_F32_ACC)
-                        reinterpret_cast<float*>(a.Y)[(long)tok * a.ldy + out_f] = val;
-                }
-                if (MODE == OUT_F32_ACC && a.norm_gain != nullptr) {
-                    // The only adder of this element sees the finished residual value: it leaves x * gain for
-                    // the product after the norm, and the tile's 128 features of this token give one partial
-                    // sum of squares (four warps of this half of the epilogue, summed in warp order).
-                    float xn = 0.f;
-                    if (out_f < out_n) {
-                        xn = atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val) + val;
-                        const float g = a.norm_gain_dtype == ZLM_F32
-                                            ? reinterpret_cast<const float*>(a.norm_gain)[out_f]
-                                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.norm_gain)[out_f]);
-                        a.norm_hb[(long)tok * a.ld_hb + out_f] = __float2bfloat16_rn(xn * (g + a.norm_offset));
+            // Up to EB tokens of this warp at a time (tiles of 64 tokens and more): their partials are all requested before the first sum,
+            // their additions to the residual all issued before the first result is used, so the latencies of
+            // the cluster's shared memory and of the returning atomics are paid once per group, not per token.
+            constexpr int EB = BN >= 64 ? 2 : 1;          // narrow tiles keep their registers: three blocks an SM
+            if constexpr (EB == 1) {
+                for (int cc = c_lo + egroup; cc < c_hi && good; cc += 2) {
+                    const int tok = tok0 + cc;
+                    if (tok >= a.T) break;
+                    float part[8];
+    #pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        part[r] = r < a.splits ? ld_cluster_f32(remote[r] + 4u * (cc * TC_BM + f_local)) : 0.f;
+                    float val = part[0];
+    #pragma unroll
+                    for (int r = 1; r < 8; ++r) val += part[r];
+                    if (a.scale_ssq != nullptr) val *= inv_s[cc];
+                    val += bias_v;
+                    if (GLU) {
+                        const float up = __shfl_down_sync(0xffffffffu, val, 1);
+                        const float g = val;
+                        val = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
                     }
-                    const float sq = warp_sum(xn * xn);
-                    if (lane == 0) norm_red[egroup][q] = sq;
-                    if (egroup == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
-                    else asm volatile("bar.sync 4, 128;" ::: "memory");
-                    if (q == 0 && lane == 0)
-                        a.norm_ssq[(long)tok * a.norm_p + tile / tok_tiles] =
-                            ((norm_red[egroup][0] + norm_red[egroup][1]) + norm_red[egroup][2]) + norm_red[egroup][3];
-                    if (egroup == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
-                    else asm volatile("bar.sync 4, 128;" ::: "memory");
+                    if (writer && out_f < out_n) {
+                        if (MODE == OUT_BF16 || GLU)
+                            reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val);
+                        else if (MODE == OUT_F32_ACC && a.norm_gain == nullptr)   // one adder per element: the order is fixed
+                            atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val);
+                        else if (MODE != OUT_F32_ACC)
+                            reinterpret_cast<float*>(a.Y)[(long)tok * a.ldy + out_f] = val;
+                    }
+                    if (MODE == OUT_F32_ACC && a.norm_gain != nullptr) {
+                        // The only adder of this element sees the finished residual value: it leaves x * gain for
+                        // the product after the norm, and the tile's 128 features of this token give one partial
+                        // sum of squares (four warps of this half of the epilogue, summed in warp order).
+                        float xn = 0.f;
+                        if (out_f < out_n) {
+                            xn = atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val) + val;
+                            const float g = a.norm_gain_dtype == ZLM_F32
+                                                ? reinterpret_cast<const float*>(a.norm_gain)[out_f]
+                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.norm_gain)[out_f]);
+                            a.norm_hb[(long)tok * a.ld_hb + out_f] = __float2bfloat16_rn(xn * (g + a.norm_offset));
+                        }
+                        const float sq = warp_sum(xn * xn);
+                        if (lane == 0) norm_red[egroup][0][q] = sq;
+                        if (egroup == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+                        else asm volatile("bar.sync 4, 128;" ::: "memory");
+                        if (q == 0 && lane == 0)
+                            a.norm_ssq[(long)tok * a.norm_p + tile / tok_tiles] =
+                                ((norm_red[egroup][0][0] + norm_red[egroup][0][1]) + norm_red[egroup][0][2]) + norm_red[egroup][0][3];
+                        if (egroup == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+                        else asm volatile("bar.sync 4, 128;" ::: "memory");
+                    }
+                }
+            } else {
+                for (int cc0 = c_lo + egroup; cc0 < c_hi && good; cc0 += 2 * EB) {
+                    if (tok0 + cc0 >= a.T) break;
+                    bool live[EB];
+                    float val[EB];
+                    float part[EB][8];
+    #pragma unroll
+                    for (int u = 0; u < EB; ++u) {
+                        const int cc = cc0 + 2 * u;
+                        live[u] = cc < c_hi && tok0 + cc < a.T;          // the same for every thread of this half
+    #pragma unroll
+                        for (int r = 0; r < 8; ++r)
+                            part[u][r] = (live[u] && r < a.splits) ? ld_cluster_f32(remote[r] + 4u * (cc * TC_BM + f_local)) : 0.f;
+                    }
+    #pragma unroll
+                    for (int u = 0; u < EB; ++u) {
+                        const int cc = cc0 + 2 * u;
+                        float v = part[u][0];
+    #pragma unroll
+                        for (int r = 1; r < 8; ++r) v += part[u][r];     // in rank order
+                        if (a.scale_ssq != nullptr) v *= inv_s[cc & 63];
+                        v += bias_v;
+                        if (GLU) {
+                            const float up = __shfl_down_sync(0xffffffffu, v, 1);
+                            const float g = v;
+                            v = gated_activation<MODE == OUT_BF16_GEGLU>(g) * up;
+                        }
+                        val[u] = v;
+                    }
+                    float before[EB];
+    #pragma unroll
+                    for (int u = 0; u < EB; ++u) {
+                        const int tok = tok0 + cc0 + 2 * u;
+                        before[u] = 0.f;
+                        if (!live[u] || !writer || out_f >= out_n) continue;
+                        if (MODE == OUT_BF16 || GLU)
+                            reinterpret_cast<__nv_bfloat16*>(a.Y)[(long)tok * a.ldy + out_f] = __float2bfloat16_rn(val[u]);
+                        else if (MODE == OUT_F32_ACC && a.norm_gain == nullptr)   // one adder per element: the order is fixed
+                            atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val[u]);
+                        else if (MODE == OUT_F32_ACC)
+                            before[u] = atomicAdd(reinterpret_cast<float*>(a.Y) + (long)tok * a.ldy + out_f, val[u]);
+                        else
+                            reinterpret_cast<float*>(a.Y)[(long)tok * a.ldy + out_f] = val[u];
+                    }
+                    if (MODE == OUT_F32_ACC && a.norm_gain != nullptr) {
+                        // The only adder of an element sees the finished residual value: it leaves x * gain for
+                        // the product after the norm, and the tile's 128 features of a token give one partial
+                        // sum of squares (four warps of this half of the epilogue, summed in warp order).
+                        float g = 0.f;
+                        if (out_f < out_n)
+                            g = (a.norm_gain_dtype == ZLM_F32
+                                     ? reinterpret_cast<const float*>(a.norm_gain)[out_f]
+                                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.norm_gain)[out_f])) + a.norm_offset;
+    #pragma unroll
+                        for (int u = 0; u < EB; ++u) {
+                            float xn = 0.f;
+                            if (live[u] && out_f < out_n) {
+                                xn = before[u] + val[u];
+                                a.norm_hb[(long)(tok0 + cc0 + 2 * u) * a.ld_hb + out_f] = __float2bfloat16_rn(xn * g);
+                            }
+                            const float sq = warp_sum(xn * xn);
+                            if (lane == 0) norm_red[egroup][u][q] = sq;
+                        }
+                        if (egroup == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+                        else asm volatile("bar.sync 4, 128;" ::: "memory");
+                        if (q == 0 && lane < EB && cc0 + 2 * lane < c_hi && tok0 + cc0 + 2 * lane < a.T)
+                            a.norm_ssq[(long)(tok0 + cc0 + 2 * lane) * a.norm_p + tile / tok_tiles] =
+                                ((norm_red[egroup][lane][0] + norm_red[egroup][lane][1]) + norm_red[egroup][lane][2]) +
+                                norm_red[egroup][lane][3];
+                        if (egroup == 0) asm volatile("bar.sync 3, 128;" ::: "memory");
+                        else asm volatile("bar.sync 4, 128;" ::: "memory");
+                    }
                 }
             }
         } else
