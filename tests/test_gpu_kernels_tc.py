@@ -39,7 +39,7 @@ def test_gemm_tc_shapes(K, T, N, K_, out_dtype):
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
-@pytest.mark.parametrize("T", [1, 8, 33, 64])
+@pytest.mark.parametrize("T", [1, 8, 33, 41, 64])
 def test_gemm_tc_split_k_is_exact_in_order(K, splits, T):
     """K split over the CTAs of a cluster: same result whatever the number of splits, up to the order of float sums;
     and the same bits every time."""
@@ -367,7 +367,7 @@ def test_tc_attention_refuses_other_head_sizes(K):
     assert K.attention_prefill(q, out, 1, 1, 1, 1, 48, 1.0, None, z, z, z.view(1, 2), pages, pages, 64) is False
 
 
-@pytest.mark.parametrize("T", [1, 8, 17, 64])
+@pytest.mark.parametrize("T", [1, 8, 17, 41, 50, 64])
 @pytest.mark.parametrize("d,k1,n2", [(256, 2048, 640), (4096, 512, 256), (200, 1024, 136), (256, 128, 64)])
 @pytest.mark.parametrize("gain_dtype", [torch.float32, BF])
 def test_gemm_tc_carries_an_rmsnorm_between_two_products(K, T, d, k1, n2, gain_dtype):
