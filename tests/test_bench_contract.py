@@ -68,3 +68,39 @@ def test_byte_and_flop_counts():
     flops += 2 * 4096 * 128256
     assert abs(bench.prefill_flops(cfg, 32, T) - flops) <= 1e-9 * flops
     assert abs(flops - 29.69e12) < 0.01e12
+
+
+import pytest
+
+
+@pytest.mark.gpu
+def test_the_line_of_a_shallow_run_has_every_key_of_the_contract():
+    """`bench.py` on two layers of the benchmarked shape: one JSON line with the metric, the end-to-end figure and
+    its bytes, the prefill and roofline records, the points, the clocks, a launch count that is the kernels of the
+    timed steps, and a flat `config` of at most 20 keys that names both layer counts."""
+    r = run("--layers", "2", "--steps", "4", "--warmup", "3")
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.strip().splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "prefill", "roofline", "points",
+                "clocks", "wait_errors"):
+        assert key in d, key
+    assert d["n_gpus"] == 1 and d["steps"] == 4 and d["warmup"] == 3 and d["higher_is_better"] is True
+    assert abs(d["value"] - 8 / d["ms_per_step"] * 1e3) < 1e-2 * d["value"]
+    cfg = d["config"]
+    assert len(cfg) <= 20 and all(not isinstance(v, (dict, list)) for v in cfg.values())
+    assert cfg["layers"] == 2 and cfg["layers_of_config"] == 32 and cfg["global_batch"] == 8 and cfg["seq_len"] == 4096
+    assert set(d["e2e"]) >= {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"}
+    assert d["e2e"]["h2d_bytes_per_step"] > 0 and d["e2e"]["d2h_bytes_per_step"] == 8 * 4
+    assert 0 < d["e2e"]["value"] <= 1.05 * d["value"]
+    assert set(d["prefill"]) >= {"value", "tokens", "ms", "frac"} and d["prefill"]["tokens"] == 2048
+    assert set(d["roofline"]) >= {"bound", "achieved", "peak", "unit", "frac"} and d["roofline"]["bound"] == "hbm"
+    assert abs(d["roofline"]["frac"] - d["roofline"]["achieved"] / d["roofline"]["peak"]) < 1e-3
+    assert {"decode_b1", "decode_b64"} <= set(d["points"])
+    assert set(d["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
+    # a decode step of two layers at these widths: embedding, first norm, five launches a layer, last norm, head,
+    # the greedy choice
+    assert d["gpu_launches"] == 4 * (5 * 2 + 5)
+    assert d["wait_errors"] == [0, 0, 0]
