@@ -73,8 +73,17 @@ TINY_G = {
     "max_position_embeddings": 256, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
     "attention_bias": True, "mlp_bias": True,
 }
-NORM_JITTER = {"A": 0.0, "B": 0.1, "C": 0.1, "D": 0.1, "E": 0.1, "F": 0.1, "G": 0.1}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F, "G": TINY_G}
+# One with a sliding window in every layer (position p sees the 48 positions up to p), at a head size the
+# tensor-core attention kernels take: prompts longer than the window, pages given back while decoding.
+TINY_H = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "hidden_size": 256, "intermediate_size": 344, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 320,
+    "rope_theta": 10000.0, "max_position_embeddings": 512, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "attention_bias": False, "sliding_window": 48,
+}
+NORM_JITTER = {"A": 0.0, "B": 0.1, "C": 0.1, "D": 0.1, "E": 0.1, "F": 0.1, "G": 0.1, "H": 0.1}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F, "G": TINY_G, "H": TINY_H}
 
 
 def make_folder(tmp_path, cfg: dict, seed: int, dtype: torch.dtype, norm_jitter: float = 0.0, std: float = 0.02) -> str:

@@ -62,6 +62,14 @@ def test_what_config_json_allows_beyond_the_usual_checkpoints():
     assert config_from_dict(cfg).rope_scaling.rope_type == "linear"
     cfg["rope_scaling"] = {"rope_type": "default"}
     assert config_from_dict(cfg).rope_scaling is None
+    # a sliding window is every layer's; null and an absent key mean every earlier position
+    h = config_from_dict(helpers.TINY_H)
+    assert h.sliding_window == 48 and all(layer.mixer.window == 48 for layer in h.model_spec().layers)
+    assert h.to_dict()["sliding_window"] == 48
+    cfg = copy.deepcopy(helpers.TINY_H)
+    cfg["sliding_window"] = None
+    assert config_from_dict(cfg).sliding_window is None and config_from_dict(cfg).model_spec().layers[0].mixer.window is None
+    assert "sliding_window" not in config_from_dict(helpers.TINY_A).to_dict()
 
 
 def test_helpers_of_a_configuration_class_belong_to_no_architecture():
@@ -98,7 +106,7 @@ def test_missing_required_key(key):
     ({"rope_scaling": {"rope_type": "linear", "factor": 0.5}}, "at least 1"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0, "mscale": 0.7}}, "mscale"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0, "beta_fast": 1.0, "beta_slow": 2.0}}, "beta_fast"),
-    ({"mlp_bias": "yes"}, "mlp_bias"),
+    ({"mlp_bias": "yes"}, "mlp_bias"), ({"sliding_window": 0}, "sliding_window"), ({"sliding_window": "all"}, "sliding_window"),
     ({"hidden_act": "gelu"}, "hidden_act"), ({"tie_word_embeddings": "yes"}, "tie_word_embeddings"),
     ({"head_dim": 15}, "even"), ({"eos_token_id": "x"}, "eos_token_id"),
     ({"hidden_size": 66, "head_dim": None}, "multiple"),

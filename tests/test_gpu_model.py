@@ -13,7 +13,7 @@ DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 # request lengths per configuration: a one-token request, lengths around the page size of 64, a long one
 LENGTHS = {"A": [5, 11, 17, 70, 45, 128], "B": [1, 9, 23, 40, 97, 64], "C": [3, 65, 33, 128, 12, 50],
            "D": [5, 130, 64, 200, 17, 96], "E": [1, 129, 70, 33, 250, 16], "F": [2, 66, 150, 31, 128, 90],
-           "G": [1, 40, 77, 130, 64, 19]}
+           "G": [1, 40, 77, 130, 64, 19], "H": [3, 130, 64, 200, 49, 96]}
 
 
 class Zoo:
@@ -55,7 +55,8 @@ def zoo(tmp_path_factory):
 # D and E have the head sizes of the tensor-core attention kernels: in bfloat16 their prompts run the tcgen05
 # kernel (or the mma.sync one below 16 tokens) and their decode steps the flat kernel with rotation and cache write
 # F (feed-forward biases, linear position stretching) and G (yarn) are what config.json allows beyond the usual
-CASES = [(n, d) for n in ("A", "B", "C", "F", "G") for d in ("float32", "bfloat16")] + [
+# H has a sliding window in every layer (from config.json): pages behind it are given back as a sequence grows
+CASES = [(n, d) for n in ("A", "B", "C", "F", "G", "H") for d in ("float32", "bfloat16")] + [
     ("D", "bfloat16"), ("E", "bfloat16"), ("D", "float32")]
 
 

@@ -15,7 +15,7 @@ import helpers
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LENGTHS = {"A": [5, 11, 17, 70, 45], "B": [1, 9, 23, 40, 97]}
+LENGTHS = {"A": [5, 11, 17, 70, 45], "B": [1, 9, 23, 40, 97], "H": [7, 128, 50, 100, 66]}
 
 
 class Replay:
@@ -46,7 +46,7 @@ class Replay:
         assert self.proc.wait(timeout=120) == 0
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "H"])          # H: a sliding window of 48 in every layer
 @pytest.mark.parametrize("dn", ["float32", "bfloat16"])
 def test_replay_schedules(tmp_path, name, dn):
     dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dn]

@@ -127,6 +127,7 @@ class LlamaConfig:
     attention_bias: bool = False
     mlp_bias: bool = False
     hidden_act: str = "silu"
+    sliding_window: Optional[int] = None     # position p sees [p - window + 1, p] in every layer (src/model.zig:660-661)
     bos_token_id: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
 
@@ -157,6 +158,9 @@ class LlamaConfig:
         act = d.get("hidden_act", "silu")
         if act not in ("silu", "swish"):
             raise ConfigError(f"config.json: hidden_act {act!r} is not supported by this architecture (silu)")
+        window = d.get("sliding_window")
+        if window is not None:
+            window = need_int(d, "sliding_window")
         bos = d.get("bos_token_id")
         if bos is not None and (isinstance(bos, bool) or not isinstance(bos, int)):
             raise ConfigError(f"config.json: 'bos_token_id' must be an integer, found {bos!r}")
@@ -177,6 +181,7 @@ class LlamaConfig:
             attention_bias=need_bool(d, "attention_bias", False),
             mlp_bias=need_bool(d, "mlp_bias", False),
             hidden_act="silu",
+            sliding_window=window,
             bos_token_id=bos,
             eos_token_ids=token_ids(d, "eos_token_id"),
         )
@@ -207,6 +212,8 @@ class LlamaConfig:
             "mlp_bias": self.mlp_bias,
             "hidden_act": self.hidden_act,
         }
+        if self.sliding_window is not None:
+            d["sliding_window"] = self.sliding_window
         if self.bos_token_id is not None:
             d["bos_token_id"] = self.bos_token_id
         if self.eos_token_ids:
@@ -231,7 +238,7 @@ class LlamaConfig:
                 mixer=MixerSpec(kind="attention", width=d, n_heads=self.num_attention_heads,
                                 n_kv_heads=self.num_key_value_heads, head_dim=self.head_dim,
                                 bias=self.attention_bias, out_bias=self.attention_bias,
-                                position=position),
+                                position=position, window=self.sliding_window),
                 ffn_norm=NormSpec("rmsnorm", d, self.rms_norm_eps),
                 ffn=FeedForwardSpec(kind="gated_mlp", width=d, intermediate=self.intermediate_size,
                                     activation="silu", bias=self.mlp_bias),
