@@ -211,7 +211,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
     """Logits [T, vocab] of one whole sequence: embedding, layers, final norm, head (tied to the embedding when
     there is no lm_head) (src/model.zig:495-503,543-802)."""
     hd = head_dim_of(cfg)
-    inv_freq = rope_inverse_frequencies(hd, float(cfg.get("rope_theta", 10000.0)), cfg.get("rope_scaling"),
+    rot = int(hd * float(cfg.get("partial_rotary_factor", 1.0)))    # the rotated part of a head (src/model.zig:571-572)
+    inv_freq = rope_inverse_frequencies(rot, float(cfg.get("rope_theta", 10000.0)), cfg.get("rope_scaling"),
                                         cfg.get("max_position_embeddings", 2048))
     positions = list(range(len(tokens)))
     x = embedding(tokens, w["model.embed_tokens.weight"])

@@ -62,6 +62,19 @@ def test_what_config_json_allows_beyond_the_usual_checkpoints():
     assert config_from_dict(cfg).rope_scaling.rope_type == "linear"
     cfg["rope_scaling"] = {"rope_type": "default"}
     assert config_from_dict(cfg).rope_scaling is None
+    # part of a head rotated; theta and the rule under "rope_parameters" (which wins over the separate keys)
+    cfg = copy.deepcopy(helpers.TINY_D)
+    cfg["partial_rotary_factor"] = 0.5
+    cfg["rope_theta"] = 3e4
+    cfg["rope_parameters"] = {"rope_type": "llama3", "rope_theta": 5e5, "factor": 8.0, "low_freq_factor": 1.0,
+                              "high_freq_factor": 4.0, "original_max_position_embeddings": 64}
+    c = config_from_dict(cfg)
+    assert c.rotary_dim == 32 and c.rope_theta == 5e5 and c.rope_scaling.rope_type == "llama3"
+    assert c.model_spec().layers[0].mixer.position.rotary_dim == 32
+    assert config_from_dict(json.loads(json.dumps(c.to_dict()))) == c
+    cfg["rope_parameters"] = {"rope_type": "default"}
+    c = config_from_dict(cfg)
+    assert c.rope_theta == 3e4 and c.rope_scaling is None
     # a sliding window is every layer's; null and an absent key mean every earlier position
     h = config_from_dict(helpers.TINY_H)
     assert h.sliding_window == 48 and all(layer.mixer.window == 48 for layer in h.model_spec().layers)
@@ -106,7 +119,8 @@ def test_missing_required_key(key):
     ({"rope_scaling": {"rope_type": "linear", "factor": 0.5}}, "at least 1"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0, "mscale": 0.7}}, "mscale"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0, "beta_fast": 1.0, "beta_slow": 2.0}}, "beta_fast"),
-    ({"mlp_bias": "yes"}, "mlp_bias"), ({"sliding_window": 0}, "sliding_window"), ({"sliding_window": "all"}, "sliding_window"),
+    ({"mlp_bias": "yes"}, "mlp_bias"), ({"sliding_window": 0}, "sliding_window"), ({"partial_rotary_factor": 1.5}, "partial_rotary_factor"),
+    ({"partial_rotary_factor": 0.01}, "rotated"), ({"rope_parameters": "llama3"}, "rope_parameters"), ({"sliding_window": "all"}, "sliding_window"),
     ({"hidden_act": "gelu"}, "hidden_act"), ({"tie_word_embeddings": "yes"}, "tie_word_embeddings"),
     ({"head_dim": 15}, "even"), ({"eos_token_id": "x"}, "eos_token_id"),
     ({"hidden_size": 66, "head_dim": None}, "multiple"),

@@ -1,7 +1,7 @@
 """Sizes that the configuration allows and no checkpoint of the family has: every head size in steps of 16 up
 to 256, one key/value head for seven or seventeen query heads, every head its own, widths that are no multiple
 of eight (rows of bfloat16 weights then start on no 16-byte boundary, which the tensor-core products' copies
-need), a vocabulary of two.  Each runs prompts of unequal lengths in one step and then five tokens each, in
+need), a vocabulary of two, heads of which only a part is rotated.  Each runs prompts of unequal lengths in one step and then five tokens each, in
 float32 and in bfloat16, against the plain implementation: a kernel takes the size or hands it to one that does,
 never a wrong result."""
 import warnings
@@ -14,8 +14,8 @@ import helpers
 pytestmark = pytest.mark.gpu
 
 
-def cfg(hidden, inter, heads, kv, head_dim, vocab, layers=2, tie=False, bias=False, mlp_bias=False):
-    return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": hidden,
+def cfg(hidden, inter, heads, kv, head_dim, vocab, layers=2, tie=False, bias=False, mlp_bias=False, **more):
+    return {**more, "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": hidden,
             "intermediate_size": inter, "num_hidden_layers": layers, "num_attention_heads": heads,
             "num_key_value_heads": kv, "head_dim": head_dim, "vocab_size": vocab, "rope_theta": 10000.0,
             "max_position_embeddings": 512, "rms_norm_eps": 1e-5, "tie_word_embeddings": tie,
@@ -34,6 +34,12 @@ ODD = {
     "9 heads of 64 in groups of 3; 4097 ids": cfg(264, 1000, 9, 3, 64, 4097),
     "5 heads of 128, each its own; 50001 ids": cfg(520, 1384, 5, 5, 128, 50001, layers=1),
     "width 1, two ids": cfg(1, 1, 1, 1, 16, 2),
+    # part of a head rotated (pairs (i, i + rot/2) of its first rot elements, the rest as it is): 32 of 64 and 32 of
+    # 128 (the decode kernel rotates them itself), 24 of 48 (the rotation kernel)
+    "half of a head of 64 rotated": cfg(256, 344, 4, 2, 64, 300, partial_rotary_factor=0.5),
+    "a quarter of a head of 128 rotated": cfg(384, 512, 3, 1, 128, 300, partial_rotary_factor=0.25,
+                                             rope_parameters={"rope_type": "linear", "factor": 2.0, "rope_theta": 50000.0}),
+    "half of a head of 48 rotated": cfg(144, 200, 3, 3, 48, 211, partial_rotary_factor=0.5),
 }
 
 

@@ -122,6 +122,7 @@ class LlamaConfig:
     rms_norm_eps: float = 1e-5
     rope_theta: float = 10000.0
     rope_scaling: Optional[RopeScaling] = None
+    partial_rotary_factor: float = 1.0       # the first head_dim * factor elements of a head are rotated (src/model.zig:571-572)
     max_position_embeddings: int = 2048
     tie_word_embeddings: bool = False
     attention_bias: bool = False
@@ -155,6 +156,25 @@ class LlamaConfig:
                 f"config.json: num_attention_heads {heads} is not a multiple of num_key_value_heads {kv_heads}")
         if head_dim % 2:
             raise ConfigError(f"config.json: head_dim {head_dim} must be even for rotary positions")
+        # Newer files keep theta and the stretching rule together under "rope_parameters"; it wins over the two
+        # separate keys.
+        rope = d.get("rope_parameters")
+        scaling_src = d.get("rope_scaling")
+        theta_src: Mapping[str, Any] = d
+        partial_src: Mapping[str, Any] = d
+        if rope is not None:
+            if not isinstance(rope, Mapping):
+                raise ConfigError(f"config.json: 'rope_parameters' must be an object, found {rope!r}")
+            if rope.get("rope_theta") is not None:
+                theta_src = rope
+            if rope.get("partial_rotary_factor") is not None:
+                partial_src = rope
+            scaling_src = {k: v for k, v in rope.items() if k not in ("rope_theta", "partial_rotary_factor")} or None
+        partial = need_float(partial_src, "partial_rotary_factor", default=1.0)
+        rotary = int(head_dim * partial)
+        if partial > 1.0 or rotary < 2 or rotary % 2:
+            raise ConfigError(f"config.json: partial_rotary_factor {partial} of head_dim {head_dim} gives {rotary} "
+                              "rotated elements; an even number from 2 to head_dim is needed")
         act = d.get("hidden_act", "silu")
         if act not in ("silu", "swish"):
             raise ConfigError(f"config.json: hidden_act {act!r} is not supported by this architecture (silu)")
@@ -174,8 +194,9 @@ class LlamaConfig:
             head_dim=head_dim,
             vocab_size=need_int(d, "vocab_size"),
             rms_norm_eps=need_float(d, "rms_norm_eps", default=1e-5),
-            rope_theta=need_float(d, "rope_theta", default=10000.0),
-            rope_scaling=RopeScaling.from_dict(d.get("rope_scaling"), need_int(d, "max_position_embeddings", default=2048)),
+            rope_theta=need_float(theta_src, "rope_theta", default=10000.0),
+            rope_scaling=RopeScaling.from_dict(scaling_src, need_int(d, "max_position_embeddings", default=2048)),
+            partial_rotary_factor=partial,
             max_position_embeddings=need_int(d, "max_position_embeddings", default=2048),
             tie_word_embeddings=need_bool(d, "tie_word_embeddings", False),
             attention_bias=need_bool(d, "attention_bias", False),
@@ -212,6 +233,8 @@ class LlamaConfig:
             "mlp_bias": self.mlp_bias,
             "hidden_act": self.hidden_act,
         }
+        if self.partial_rotary_factor != 1.0:
+            d["partial_rotary_factor"] = self.partial_rotary_factor
         if self.sliding_window is not None:
             d["sliding_window"] = self.sliding_window
         if self.bos_token_id is not None:
@@ -220,6 +243,10 @@ class LlamaConfig:
             d["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         return d
 
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
+
     # ----------------------------------------------------------- model structure
     def model_spec(self) -> ModelSpec:
         """Lay the architecture out as parts: L identical pre-norm blocks of
@@ -227,7 +254,7 @@ class LlamaConfig:
         (src/model.zig:543-789 is the reference's layer loop)."""
         d = self.hidden_size
         scaling = self.rope_scaling.to_dict() if self.rope_scaling else None
-        position = PositionSpec(kind="rope", rotary_dim=self.head_dim, theta=self.rope_theta,
+        position = PositionSpec(kind="rope", rotary_dim=self.rotary_dim, theta=self.rope_theta,
                                 scaling=scaling, max_positions=self.max_position_embeddings)
         layers = []
         for i in range(self.num_hidden_layers):
