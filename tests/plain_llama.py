@@ -163,14 +163,22 @@ def silu(z: torch.Tensor) -> torch.Tensor:
     return z / (1.0 + torch.exp(-z))
 
 
+def gelu_tanh(z: torch.Tensor) -> torch.Tensor:
+    """0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) (src/math.zig:1119-1123)."""
+    return 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z * z * z)))
+
+
 def swiglu(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
            act: Optional[torch.dtype], gate_bias: Optional[torch.Tensor] = None,
-           up_bias: Optional[torch.Tensor] = None, down_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """f = W_d (silu(W_g x) * (W_u x)) (src/model.zig:725-745, src/math.zig:1112-1117); the architecture's
+           up_bias: Optional[torch.Tensor] = None, down_bias: Optional[torch.Tensor] = None,
+           hidden_act: str = "silu") -> torch.Tensor:
+    """f = W_d (silu(W_g x) * (W_u x)) (src/model.zig:725-745, src/math.zig:1112-1117), or with the tanh form of
+    gelu in silu's place where config.json's hidden_act says so (src/math.zig:1125-1130); the architecture's
     mlp_bias adds a bias to each of the three products (the reference has none)."""
     g = _round(linear(x, gate, gate_bias), act)
     u = _round(linear(x, up, up_bias), act)
-    a = _round(silu(g) * u, act)
+    gated = silu(g) if hidden_act in ("silu", "swish") else gelu_tanh(g)
+    a = _round(gated * u, act)
     return linear(a, down, down_bias)
 
 
@@ -202,7 +210,7 @@ def decoder_layer(cfg: dict, w: Dict[str, torch.Tensor], i: int, x: torch.Tensor
     mb = cfg.get("mlp_bias", False)
     x = x + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"], act,
                    w[p + "mlp.gate_proj.bias"] if mb else None, w[p + "mlp.up_proj.bias"] if mb else None,
-                   w[p + "mlp.down_proj.bias"] if mb else None)
+                   w[p + "mlp.down_proj.bias"] if mb else None, cfg.get("hidden_act", "silu"))
     return x
 
 

@@ -75,6 +75,12 @@ def test_what_config_json_allows_beyond_the_usual_checkpoints():
     cfg["rope_parameters"] = {"rope_type": "default"}
     c = config_from_dict(cfg)
     assert c.rope_theta == 3e4 and c.rope_scaling is None
+    # the gate's activation: silu, or the tanh form of gelu
+    cfg = copy.deepcopy(helpers.TINY_D)
+    cfg["hidden_act"] = "gelu_pytorch_tanh"
+    c = config_from_dict(cfg)
+    assert c.model_spec().layers[0].ffn.activation == "gelu_tanh" and c.to_dict()["hidden_act"] == "gelu_pytorch_tanh"
+    assert config_from_dict(helpers.TINY_D).model_spec().layers[0].ffn.activation == "silu"
     # a sliding window is every layer's; null and an absent key mean every earlier position
     h = config_from_dict(helpers.TINY_H)
     assert h.sliding_window == 48 and all(layer.mixer.window == 48 for layer in h.model_spec().layers)
@@ -121,7 +127,7 @@ def test_missing_required_key(key):
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0, "beta_fast": 1.0, "beta_slow": 2.0}}, "beta_fast"),
     ({"mlp_bias": "yes"}, "mlp_bias"), ({"sliding_window": 0}, "sliding_window"), ({"partial_rotary_factor": 1.5}, "partial_rotary_factor"),
     ({"partial_rotary_factor": 0.01}, "rotated"), ({"rope_parameters": "llama3"}, "rope_parameters"), ({"sliding_window": "all"}, "sliding_window"),
-    ({"hidden_act": "gelu"}, "hidden_act"), ({"tie_word_embeddings": "yes"}, "tie_word_embeddings"),
+    ({"hidden_act": "gelu"}, "hidden_act"), ({"hidden_act": "relu"}, "hidden_act"), ({"tie_word_embeddings": "yes"}, "tie_word_embeddings"),
     ({"head_dim": 15}, "even"), ({"eos_token_id": "x"}, "eos_token_id"),
     ({"hidden_size": 66, "head_dim": None}, "multiple"),
 ])

@@ -40,6 +40,9 @@ ODD = {
     "a quarter of a head of 128 rotated": cfg(384, 512, 3, 1, 128, 300, partial_rotary_factor=0.25,
                                              rope_parameters={"rope_type": "linear", "factor": 2.0, "rope_theta": 50000.0}),
     "half of a head of 48 rotated": cfg(144, 200, 3, 3, 48, 211, partial_rotary_factor=0.5),
+    # the tanh form of gelu in the gate's place, with biases; at a head size and width that take the fused product
+    "gelu gate": cfg(256, 344, 4, 2, 64, 300, mlp_bias=True, hidden_act="gelu_pytorch_tanh"),
+    "gelu gate, narrow": cfg(72, 77, 3, 3, 32, 31, hidden_act="gelu_pytorch_tanh"),
 }
 
 

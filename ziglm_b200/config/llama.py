@@ -176,8 +176,13 @@ class LlamaConfig:
             raise ConfigError(f"config.json: partial_rotary_factor {partial} of head_dim {head_dim} gives {rotary} "
                               "rotated elements; an even number from 2 to head_dim is needed")
         act = d.get("hidden_act", "silu")
-        if act not in ("silu", "swish"):
-            raise ConfigError(f"config.json: hidden_act {act!r} is not supported by this architecture (silu)")
+        if act in ("silu", "swish"):
+            act = "silu"
+        elif act in ("gelu_pytorch_tanh", "gelu_tanh"):
+            act = "gelu_pytorch_tanh"                    # the tanh form (src/math.zig:1119-1123)
+        else:
+            raise ConfigError(f"config.json: hidden_act {act!r} is not supported by this architecture "
+                              "(silu, gelu_pytorch_tanh)")
         window = d.get("sliding_window")
         if window is not None:
             window = need_int(d, "sliding_window")
@@ -201,7 +206,7 @@ class LlamaConfig:
             tie_word_embeddings=need_bool(d, "tie_word_embeddings", False),
             attention_bias=need_bool(d, "attention_bias", False),
             mlp_bias=need_bool(d, "mlp_bias", False),
-            hidden_act="silu",
+            hidden_act=act,
             sliding_window=window,
             bos_token_id=bos,
             eos_token_ids=token_ids(d, "eos_token_id"),
@@ -268,7 +273,8 @@ class LlamaConfig:
                                 position=position, window=self.sliding_window),
                 ffn_norm=NormSpec("rmsnorm", d, self.rms_norm_eps),
                 ffn=FeedForwardSpec(kind="gated_mlp", width=d, intermediate=self.intermediate_size,
-                                    activation="silu", bias=self.mlp_bias),
+                                    activation="silu" if self.hidden_act == "silu" else "gelu_tanh",
+                                    bias=self.mlp_bias),
                 names={
                     "mixer_norm.weight": "input_layernorm.weight",
                     "mixer.q.weight": "self_attn.q_proj.weight",
