@@ -102,6 +102,27 @@ def test_replay_schedules(tmp_path, name, dn):
         rp.close()
 
 
+@pytest.mark.parametrize("dn", ["float32", "bfloat16"])
+def test_replay_runs_positions_beyond_those_the_configuration_names(tmp_path, dn):
+    """A trace checks arithmetic: a request may be as long as the cache it was given, although config.json says the
+    model knows 64 positions (the rotation of a position is defined for every position; llama3 stretching reads
+    its own original length, not this one)."""
+    dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dn]
+    cfg = dict(helpers.TINY_B, max_position_embeddings=64)
+    folder = helpers.make_folder(tmp_path, cfg, 33, dtype, 0.1)
+    r = helpers.random_tokens(150, cfg["vocab_size"], 77)
+    want = helpers.plain_logits(folder, r, act=None if dn == "float32" else torch.bfloat16)
+    rp = Replay(folder, dn, str(tmp_path / "logits"), max_tokens=192)
+    try:
+        got = rp.step([{"id": "a", "tokens": r[:140], "want": list(range(140))}])
+        helpers.assert_close(got, want[:140], dtype, f"{dn} prompt past position 64")
+        for p in range(140, 150):
+            got = rp.step([{"id": "a", "tokens": [r[p]], "want": [0]}], end=["a"] if p == 149 else [])
+            helpers.assert_close(got, want[p:p + 1], dtype, f"{dn} position {p}")
+    finally:
+        rp.close()
+
+
 def test_replay_from_a_fresh_checkout_as_another_user(tmp_path):
     """A copy of the sources without built files, run with an empty HOME: what has to be compiled is compiled at
     the first call, with a line now and then on standard error."""

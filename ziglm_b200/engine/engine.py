@@ -47,6 +47,9 @@ class EngineOptions:
                  whole pages of 64; default max_batch * max_seq_len.
     max_batch    most sequences alive at once (slots).
     device       CUDA device.
+    beyond_max_positions  let ``max_seq_len`` pass the model's max_position_embeddings: the rotation is a function
+                 of the position alone, so the arithmetic is defined there; what a model makes of positions it was
+                 not trained on is its user's concern (replay, which checks arithmetic, sets it).
     """
     num_threads: Optional[int] = None
     max_seq_len: Optional[int] = None
@@ -57,6 +60,7 @@ class EngineOptions:
     max_batch: int = 8
     device: str = "cuda:0"
     use_graphs: bool = True
+    beyond_max_positions: bool = False
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
@@ -82,7 +86,7 @@ class Engine:
         self.dtype = model.dtype
         limit = self.spec.max_positions or 4096
         self.max_seq_len = int(options.max_seq_len) if options.max_seq_len else min(limit, 4096)
-        if self.spec.max_positions and self.max_seq_len > self.spec.max_positions:
+        if self.spec.max_positions and self.max_seq_len > self.spec.max_positions and not options.beyond_max_positions:
             raise ValueError(f"max_seq_len {self.max_seq_len} exceeds the model's max_position_embeddings "
                              f"{self.spec.max_positions}")
         max_tokens = options.max_tokens or options.max_batch * (-(-self.max_seq_len // PAGE_SIZE) * PAGE_SIZE)

@@ -34,10 +34,10 @@ def main(argv: Optional[List[str]] = None, stdin=None, stdout=None) -> int:
     stdout = stdout or sys.stdout
     os.makedirs(args.out, exist_ok=True)
     max_tokens = max(PAGE_SIZE, -(-args.max_tokens // PAGE_SIZE) * PAGE_SIZE)
-    probe_cfg = json.load(open(os.path.join(args.model, "config.json"), "r", encoding="utf-8"))
-    limit = int(probe_cfg.get("max_position_embeddings") or max_tokens)
+    # a request may be as long as the cache: a trace is a check of arithmetic, and the rotation of a position is
+    # defined beyond the positions config.json says the model was trained on
     options = EngineOptions(dtype=args.dtype, max_tokens=max_tokens, max_batch=max_tokens // PAGE_SIZE,
-                            max_seq_len=min(limit, max_tokens))
+                            max_seq_len=max_tokens, beyond_max_positions=True)
     engine = Engine.load(args.model, options)
     slot_of: Dict[str, int] = {}
     for line in stdin:
