@@ -405,3 +405,35 @@ def test_a_decode_step_taken_again_is_the_same_step(zoo):
     for s in b:
         plain.free_slot(s)
     eng.cache.slots.check()
+
+
+@pytest.mark.parametrize("which", ["all", "norms"])
+def test_tensors_stored_in_32_bit_stay_so_under_the_bfloat16_engine(tmp_path, which):
+    """A folder whose tensors (all of them, or only the norms' gains) are stored in float32, run in bfloat16:
+    those tensors are kept as they are stored, activations and the cache are bfloat16, and the logits are the
+    plain model's with the same weights and activations rounded at the same places."""
+    import json
+    import os
+    from safetensors.torch import save_file
+    from ziglm_b200 import Engine, EngineOptions
+    cfg = helpers.CONFIGS["D"]
+    folder = helpers.make_folder(tmp_path, cfg, 41, torch.float32, 0.1)
+    if which == "norms":
+        _, tensors = helpers.read_folder(folder)
+        mixed = {n: (t if "norm" in n else t.to(torch.bfloat16)) for n, t in tensors.items()}
+        folder = os.path.join(str(tmp_path), "mixed")
+        os.makedirs(folder)
+        save_file(mixed, os.path.join(folder, "model.safetensors"))
+        json.dump(cfg, open(os.path.join(folder, "config.json"), "w"))
+    eng = Engine.load(folder, EngineOptions(dtype="bfloat16", max_tokens=512, max_batch=4))
+    assert eng.model.final_norm.weight.dtype == torch.float32
+    assert eng.model.embedding.dtype == (torch.float32 if which == "all" else torch.bfloat16)
+    reqs = [helpers.random_tokens(n, cfg["vocab_size"], 60 + n) for n in (150, 7, 66)]
+    want = [helpers.plain_logits(folder, r, act=torch.bfloat16) for r in reqs]
+    slots = [eng.alloc_slot() for _ in reqs]
+    cut = [len(r) - 4 for r in reqs]
+    got = eng.step([(s, r[:k]) for s, r, k in zip(slots, reqs, cut)], [list(range(k)) for k in cut]).clone()
+    helpers.assert_close(got, torch.cat([w[:k] for w, k in zip(want, cut)]), torch.bfloat16, f"{which}: prompts")
+    for j in range(4):
+        got = eng.step([(s, [r[k + j]]) for s, r, k in zip(slots, reqs, cut)]).clone()
+        helpers.assert_close(got, torch.stack([w[k + j] for w, k in zip(want, cut)]), torch.bfloat16, f"{which}: token {j}")
