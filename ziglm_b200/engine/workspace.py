@@ -19,15 +19,20 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._flat: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._last: Dict[Tuple[str, torch.dtype], Tuple[tuple, torch.Tensor]] = {}   # the view handed out last
         self.moves = 0
 
     def buf(self, name: str, shape, dtype: torch.dtype, zeros: bool = False) -> torch.Tensor:
         """The named buffer, at least as large as ``shape``.  ``zeros``: the memory is zero when it is first
         handed out (and when it has grown); afterwards it holds what its users left."""
+        key = (name, dtype)
+        shape = tuple(shape)
+        last = self._last.get(key)
+        if last is not None and last[0] == shape:
+            return last[1]                      # steps of one shape ask for the same views again and again
         n = 1
         for s in shape:
             n *= int(s)
-        key = (name, dtype)
         flat = self._flat.get(key)
         if flat is None or flat.numel() < n:
             if flat is not None:
@@ -35,7 +40,9 @@ class Workspace:
             make = torch.zeros if zeros else torch.empty
             flat = make(max(n, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
-        return flat[:n].view(*shape)
+        view = flat[:n].view(*shape)
+        self._last[key] = (shape, view)
+        return view
 
     def zero(self, name: str) -> None:
         """Set every buffer of this name to zero (whatever its element type)."""
